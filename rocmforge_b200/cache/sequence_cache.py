@@ -41,6 +41,7 @@ class KVGroup:
         self.window = request.window
         self.chunk = request.chunk
         self.drops = bool(request.window or request.chunk)     # pages fall out of every future query's sight
+        self.kept_pages = pages_for(request.keep_first)        # ... but not those of the first positions that stay visible
         self.pool = FreeList(n_pages, "cache page")
         # [owner, k|v, page, kv_head, position in page, head_dim]; values of another head size than keys have a tensor
         # of their own (storage then holds the keys alone)
@@ -87,7 +88,7 @@ class KVGroup:
             return
         keep_from = self.first_needed_page(length)
         row = self.table[slot]
-        for p in range(keep_from - 1, -1, -1):
+        for p in range(keep_from - 1, self.kept_pages - 1, -1):
             if row[p] < 0:
                 break                                   # everything below was trimmed earlier
             self.pool.give_back(int(row[p]))

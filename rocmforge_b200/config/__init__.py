@@ -4,4 +4,5 @@ from .registry import (register_architecture, architecture_for, known_architectu
 from .qwen2 import Qwen2Config
 from .rifizen import RifizenConfig
 from .vilulorn import VilulornConfig
+from .figalix import FigalixConfig
 from . import vilulorn   # (its builder registers "Vilulorn")

@@ -41,7 +41,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ seq_slot, const int* __restrict__ block_table,
                          int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                         const float* __restrict__ slopes, int window, int hpb) {
+                         const float* __restrict__ slopes, int window, int hpb, int keep_first) {
     constexpr int ACC = ATT_GB * (CK == 128 ? 256 : ATT_MAX_HD) / ATT_THREADS;     // (head, dim) pairs of a thread at most
     pdl_trigger();
     pdl_wait();
@@ -58,6 +58,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int slot = seq_slot[tok_seq[t]];
     const int* bt = block_table + (size_t)slot * max_pages;
     const int lo = rf_first_key(pos, window);
+    // with a window the first keep_first positions of the sequence stay visible for good: the keys below the window's
+    // start that lie among them are a second stretch, walked before the window's
+    const int kept = keep_first < lo ? keep_first : lo;
 
     // rows of whole 4-element groups: 16-byte (8-byte) loads
     auto load_chunk = [&](const T* __restrict__ pages, int c0, int cnt, int hd, int ldk) {
@@ -109,8 +112,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
         for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
 
-        for (int c0 = lo; c0 <= pos; c0 += CK) {
-            const int cnt = min(CK, pos - c0 + 1);
+        for (int c0 = kept > 0 ? 0 : lo; c0 <= pos; c0 = (c0 < kept && c0 + CK >= kept) ? lo : c0 + CK) {
+            const int cnt = c0 < kept ? min(CK, kept - c0) : min(CK, pos - c0 + 1);
             __syncthreads();                        // the values of the chunk before are used up (and qs is written)
             load_chunk(k_pages, c0, cnt, hd, ldk);
             __syncthreads();
@@ -217,7 +220,7 @@ template <typename T, int CK>
 static int launch_ck(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                      const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                      const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                     const float* slopes, int window, int T_, cudaStream_t st) {
+                     const float* slopes, int window, int T_, cudaStream_t st, int keep_first) {
     const int hm = hd > hdv ? hd : hdv;
     const size_t smem = ((size_t)ATT_GB * hd + (size_t)CK * (hm + 1) + ATT_GB * CK + ATT_WARPS * ATT_GB) * sizeof(float);
     static size_t configured = 0;
@@ -239,7 +242,7 @@ static int launch_ck(const void* q, int q_stride, void* out, int out_stride, con
     rf_launch(attention_generic_kernel<T, CK>, grid, dim3(ATT_THREADS), smem, st,
         reinterpret_cast<const T*>(q), q_stride, reinterpret_cast<T*>(out), out_stride,
         reinterpret_cast<const T*>(k_pages), reinterpret_cast<const T*>(v_pages), tok_seq, tok_pos, seq_slot,
-        block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, hpb);
+        block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, hpb, keep_first);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -248,14 +251,15 @@ template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                   const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                   const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                  const float* slopes, int window, int T_, cudaStream_t st) {
+                  const float* slopes, int window, int T_, cudaStream_t st, int keep_first = 0) {
     if (T_ <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (hd <= 0 || hd > ATT_MAX_HD || hdv <= 0 || hdv > ATT_MAX_HD || nkv <= 0 || nh % nkv || nkv > 65535) return RF_ERR_UNSUPPORTED;
     if (hd <= 256 && hdv <= 256)
         return launch_ck<T, 128>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                                 max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
+                                 max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
     return launch_ck<T, 64>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                            max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
+                            max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
 }
 
 extern "C" int rf_attention_generic(int dtype, const void* q, int q_stride, void* out, int out_stride,
@@ -272,15 +276,16 @@ extern "C" int rf_attention_generic(int dtype, const void* q, int q_stride, void
 
 // The same with the options of other designs: values of another head size (hdv; value pages are
 // [n_pages, nkv, RF_PAGE, hdv], the output [T, nh * hdv]), scores capped as softcap * tanh(score / softcap)
-// (softcap 0: not capped) and, after the cap, lowered by slopes[head] * (query position - key position) (slopes null: no bias).
+// (softcap 0: not capped) and, after the cap, lowered by slopes[head] * (query position - key position) (slopes null: no bias);
+// keep_first: with a window (window > 0), the first keep_first positions of a sequence stay visible as well.
 extern "C" int rf_attention_generic_ext(int dtype, const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_pages, const void* v_pages, const int* tok_seq,
                                         const int* tok_pos, const int* seq_slot, const int* block_table,
                                         int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                                        const float* slopes, int window, int T_, cudaStream_t st) {
+                                        const float* slopes, int window, int keep_first, int T_, cudaStream_t st) {
     return dtype == 0
         ? launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                        max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st)
+                        max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first)
         : launch<__nv_bfloat16>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
-                                block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
+                                block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
 }

@@ -578,7 +578,8 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
                           const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                           const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
                           T* __restrict__ v_pages, int write_kv, int rot_dim, int interleaved, int unit_norm, float eps,
-                          const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_is_f32) {
+                          const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_is_f32,
+                          float magnitude) {
     extern __shared__ float heads_buf[];            // [warps][max(hd, hdv)]
     pdl_trigger();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -627,6 +628,7 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
                 else { first = e < rh; i = first ? e : e - rh; partner = first ? e + rh : e - rh; }
                 float s, c;
                 sincosf((float)pos * inv_freq[i], &s, &c);
+                s *= magnitude; c *= magnitude;           // encodings that lengthen the rotated pairs (1: a pure rotation)
                 const float y = buf[partner] * r;
                 x = first ? x * c - y * s : x * c + y * s;
             }
@@ -654,15 +656,16 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ a, 
     }
 }
 
-// ---------------------------------------------------------------- out[t, c] = x[t, c] * sigmoid(gate[t, c])
+// ---------------------------------------------------------------- out[t, c] = x[t, c] * sigmoid(gate[t, c / group])
+// group 1: a gate per element; group = a head's size: one gate per head
 template <typename T>
 __global__ void sigmoid_gate_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride,
-                                    T* __restrict__ out, size_t n, int W) {
+                                    T* __restrict__ out, size_t n, int W, int group) {
     pdl_trigger();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / W, c = idx - t * W;
-        const float g = Cvt<T>::to_f32(gate[t * gate_stride + c]);
+        const float g = Cvt<T>::to_f32(gate[t * gate_stride + c / group]);
         out[idx] = Cvt<T>::from_f32(Cvt<T>::to_f32(x[t * x_stride + c]) / (1.f + expf(-g)));
     }
 }
@@ -674,6 +677,112 @@ __global__ void round_rows_kernel(const float* __restrict__ h, T* __restrict__ o
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
         out[idx] = Cvt<T>::from_f32(h[idx]);
+}
+
+// ---------------------------------------------------------------- Dynamic Tanh: a norm without statistics
+// y = tanh(alpha h) * w + b, element by element (alpha one number), of the rows that `rows` lists (null: all).  The
+// vectors and alpha are 32-bit.
+template <typename T>
+__global__ void dyt_rows_kernel(const float* __restrict__ h, const int* __restrict__ rows, const float* __restrict__ alpha,
+                                const float* __restrict__ w, const float* __restrict__ b, T* __restrict__ y, int H) {
+    pdl_trigger();
+    const float a = alpha[0];
+    pdl_wait();
+    const size_t src = (size_t)(rows != nullptr ? rows[blockIdx.x] : (int)blockIdx.x) * H, dst = (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) y[dst + c] = Cvt<T>::from_f32(fmaf(tanhf(a * h[src + c]), w[c], b[c]));
+}
+
+// ---------------------------------------------------------------- a scaled update of the stream
+// The residual update of a block that scales its sub-layers' outputs, all in 32-bit:
+//   m = a0 (+ a1)                                     (one result, or two that are summed: w0 null), or
+//   m = (rms(a0) * w0 + rms(a1) * w1) / 2             (two branches side by side, each normed with its own weight)
+//   h += mult * m
+//   y_next = tanh(alpha h) * w_next + b_next          in the compute dtype, if the caller knows the norm that reads the
+//                                                      stream next (a Dynamic Tanh)
+// with rms(x) = x / sqrt(mean(x^2) + eps).  a0 (a1) comes as n0 (n1) partial sums [n][rows][H] of a K-split product,
+// added here in index order.  A block per row.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+scaled_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int n0, const void* __restrict__ w0,
+                  const float* __restrict__ a1, int n1, size_t part_stride, const void* __restrict__ w1, int w_is_f32,
+                  float eps, float mult, const float* __restrict__ alpha, const float* __restrict__ w_next,
+                  const float* __restrict__ b_next, T* __restrict__ y_next, int H) {
+    extern __shared__ float row[];                  // [H], a second [H] for the other branch, 34 for the sums
+    float* other = row + H;
+    float* red = other + H;
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * H;
+    const float invH = 1.f / (float)H;
+    const float a = y_next != nullptr ? alpha[0] : 0.f;
+    pdl_wait();
+    float s0 = 0.f, s1 = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float x = 0.f, z = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
+        if (a1 != nullptr) {
+#pragma unroll 4
+            for (int s = 0; s < n1; ++s) z += a1[(size_t)s * part_stride + base + c];
+        }
+        row[c] = x; other[c] = z;
+        s0 += x * x; s1 += z * z;
+    }
+    float r0 = 1.f, r1 = 1.f;
+    if (w0 != nullptr) {
+        r0 = rsqrtf(block_sum(s0, red) * invH + eps);
+        r1 = rsqrtf(block_sum(s1, red) * invH + eps);
+    }
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {      // a thread reads what it wrote
+        const float m = w0 != nullptr
+            ? 0.5f * (row[c] * r0 * load_vec(w0, w_is_f32, c) + other[c] * r1 * load_vec(w1, w_is_f32, c))
+            : row[c] + other[c];
+        const float v = fmaf(mult, m, h[base + c]);
+        h[base + c] = v;
+        if (y_next != nullptr) y_next[base + c] = Cvt<T>::from_f32(fmaf(tanhf(a * v), w_next[c], b_next[c]));
+    }
+}
+
+// ---------------------------------------------------------------- x <- cap * tanh(x / cap), in place (logits)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const float inv = 1.f / cap;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] * inv);
+}
+
+template <typename T>
+static int launch_dyt_rows(const float* h, const int* rows, const float* alpha, const float* w, const float* b, void* y, int R,
+                           int H, cudaStream_t st) {
+    if (R <= 0) return 0;
+    int threads = (H + 3) / 4;
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : (threads + 31) / 32 * 32);
+    rf_launch(dyt_rows_kernel<T>, dim3(R), dim3(threads), 0, st, h, rows, alpha, w, b, reinterpret_cast<T*>(y), H);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_scaled_add(float* h, const float* a0, int n0, const void* w0, const float* a1, int n1, const void* w1,
+                             int w_is_f32, float eps, float mult, const float* alpha, const float* w_next,
+                             const float* b_next, void* y_next, int rows, int H, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (n0 < 1 || (a1 != nullptr && n1 < 1) || (w0 != nullptr && (a1 == nullptr || w1 == nullptr))) return RF_ERR_BAD_ARG;
+    if (y_next != nullptr && (alpha == nullptr || w_next == nullptr || b_next == nullptr)) return RF_ERR_BAD_ARG;
+    const size_t smem = (size_t)(2 * H + 34) * sizeof(float);
+    if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(scaled_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    int threads = 256;
+    if (rows <= 296) { threads = (H + 31) / 32 * 32; if (threads > 1024) threads = 1024; if (threads < 256) threads = 256; }
+    rf_launch(scaled_add_kernel<T>, dim3(rows), dim3(threads), smem, st, h, a0, n0, w0, a1, n1, (size_t)rows * H, w1, w_is_f32,
+              eps, mult, alpha, w_next, b_next, reinterpret_cast<T*>(y_next), H);
+    RF_LAUNCH_CHECK();
+    return 0;
 }
 
 // ---------------------------------------------------------------- launchers
@@ -691,12 +800,13 @@ static int launch_clamped_glu(const void* gu, void* a, int T_, int I, float limi
 
 template <typename T>
 static int launch_sigmoid_gate(const void* x, int x_stride, const void* gate, int gate_stride, void* out, int T_, int W,
-                               cudaStream_t st) {
+                               int group, cudaStream_t st) {
+    if (group < 1) return RF_ERR_BAD_ARG;
     const size_t n = (size_t)T_ * W;
     if (n == 0) return 0;
     const size_t blocks = (n + 255) / 256;
     rf_launch(sigmoid_gate_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st,
-              reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n, W);
+              reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n, W, group);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -875,7 +985,8 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
                                      const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
                                      int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, int rot_dim,
                                      int interleaved, int unit_norm, float eps, cudaStream_t st,
-                                     const void* q_norm_w = nullptr, const void* k_norm_w = nullptr, int norm_w_is_f32 = 0) {
+                                     const void* q_norm_w = nullptr, const void* k_norm_w = nullptr, int norm_w_is_f32 = 0,
+                                     float magnitude = 1.f) {
     if (T_ <= 0) return 0;
     if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0) return RF_ERR_BAD_ARG;
     const size_t smem = (size_t)4 * (hd > hdv ? hd : hdv) * sizeof(float);
@@ -888,12 +999,12 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
         rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_, by), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
-                  q_norm_w, k_norm_w, norm_w_is_f32);
+                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
     else
         rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_, by), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
-                  q_norm_w, k_norm_w, norm_w_is_f32);
+                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -964,21 +1075,22 @@ int rf_head_norm_kv_write(int dtype, const void* src, int row_stride, int n_part
                                                    max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
                                                    unit_norm, eps, st);
 }
-// The same with weights of the q and k norms (each [hd], shared by the heads; null: a plain division).
+// The same with weights of the q and k norms (each [hd], shared by the heads; null: a plain division) and a factor on the
+// rotation's sine and cosine (1: a pure rotation).
 int rf_head_norm_kv_write_w(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride, void* q_out,
                             int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq, const int* tok_seq,
                             const int* tok_pos, const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
                             void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, int unit_norm, float eps,
-                            const void* q_norm_w, const void* k_norm_w, int norm_w_is_f32, cudaStream_t st) {
+                            const void* q_norm_w, const void* k_norm_w, int norm_w_is_f32, float magnitude, cudaStream_t st) {
     return dtype == 0
         ? launch_head_norm_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride, nh, nkv,
                                            hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, max_pages, k_pages,
                                            v_pages, write_kv, T_, rot_dim, interleaved, unit_norm, eps, st, q_norm_w, k_norm_w,
-                                           norm_w_is_f32)
+                                           norm_w_is_f32, magnitude)
         : launch_head_norm_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride,
                                                    nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                                                    max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
-                                                   unit_norm, eps, st, q_norm_w, k_norm_w, norm_w_is_f32);
+                                                   unit_norm, eps, st, q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
 }
 int rf_clamped_glu(int dtype, const void* gu, void* a, int T_, int I, float limit, float alpha, const float* row_scale,
                    cudaStream_t st) {
@@ -986,11 +1098,34 @@ int rf_clamped_glu(int dtype, const void* gu, void* a, int T_, int I, float limi
                       : launch_clamped_glu<__nv_bfloat16>(gu, a, T_, I, limit, alpha, row_scale, st);
 }
 int rf_sigmoid_gate(int dtype, const void* x, int x_stride, const void* gate, int gate_stride, void* out, int T_, int W,
-                    cudaStream_t st) {
-    return dtype == 0 ? launch_sigmoid_gate<float>(x, x_stride, gate, gate_stride, out, T_, W, st)
-                      : launch_sigmoid_gate<__nv_bfloat16>(x, x_stride, gate, gate_stride, out, T_, W, st);
+                    int group, cudaStream_t st) {
+    return dtype == 0 ? launch_sigmoid_gate<float>(x, x_stride, gate, gate_stride, out, T_, W, group, st)
+                      : launch_sigmoid_gate<__nv_bfloat16>(x, x_stride, gate, gate_stride, out, T_, W, group, st);
 }
 int rf_round_rows(int dtype, const float* h, void* out, long long n, cudaStream_t st) {
     return dtype == 0 ? launch_round_rows<float>(h, out, n, st) : launch_round_rows<__nv_bfloat16>(h, out, n, st);
+}
+// y [R, H] of dtype = tanh(alpha h[rows]) * w + b; rows null: every row of h [R, H]
+int rf_dyt_rows(int dtype, const float* h, const int* rows, const float* alpha, const float* w, const float* b, void* y,
+                int R, int H, cudaStream_t st) {
+    return dtype == 0 ? launch_dyt_rows<float>(h, rows, alpha, w, b, y, R, H, st)
+                      : launch_dyt_rows<__nv_bfloat16>(h, rows, alpha, w, b, y, R, H, st);
+}
+// w0 / w1 null: h += mult * (a0 + a1) (a1 null: a0 alone); else h += mult * mean of the two normed branches.  y_next
+// (of dtype) null: no next norm.  w0, w1 share w_is_f32; alpha, w_next, b_next are float.
+int rf_scaled_add(int dtype, float* h, const float* a0, int n0, const void* w0, const float* a1, int n1, const void* w1,
+                  int w_is_f32, float eps, float mult, const float* alpha, const float* w_next, const float* b_next,
+                  void* y_next, int rows, int H, cudaStream_t st) {
+    return dtype == 0
+        ? launch_scaled_add<float>(h, a0, n0, w0, a1, n1, w1, w_is_f32, eps, mult, alpha, w_next, b_next, y_next, rows, H, st)
+        : launch_scaled_add<__nv_bfloat16>(h, a0, n0, w0, a1, n1, w1, w_is_f32, eps, mult, alpha, w_next, b_next, y_next, rows, H, st);
+}
+int rf_softcap(float* x, long long n, float cap, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return RF_ERR_BAD_ARG;
+    const long long blocks = (n + 255) / 256;
+    rf_launch(softcap_kernel, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st, x, (size_t)n, cap);
+    RF_LAUNCH_CHECK();
+    return 0;
 }
 }

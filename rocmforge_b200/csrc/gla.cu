@@ -72,13 +72,40 @@ __device__ __forceinline__ void gl_token(float (&s)[ROWS], const float* __restri
     }
 }
 
+// The same with ONE decay for all rows of the head (designs whose state decays by a scalar per head and token).
+template <int ROWS>
+__device__ __forceinline__ void gl_token_scalar(float (&s)[ROWS], float a, const float* __restrict__ k,
+                                                const float* __restrict__ q, float vj, float (&out)[ROWS / GL_SLICE]) {
+#pragma unroll
+    for (int u = 0; u < ROWS / GL_SLICE; ++u) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = u * GL_SLICE; r < (u + 1) * GL_SLICE; r += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + r);
+            const float4 q4 = *reinterpret_cast<const float4*>(q + r);
+            s[r + 0] = fmaf(a, s[r + 0], k4.x * vj); acc[0] = fmaf(s[r + 0], q4.x, acc[0]);
+            s[r + 1] = fmaf(a, s[r + 1], k4.y * vj); acc[1] = fmaf(s[r + 1], q4.y, acc[1]);
+            s[r + 2] = fmaf(a, s[r + 2], k4.z * vj); acc[2] = fmaf(s[r + 2], q4.z, acc[2]);
+            s[r + 3] = fmaf(a, s[r + 3], k4.w * vj); acc[3] = fmaf(s[r + 3], q4.w, acc[3]);
+        }
+        out[u] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    }
+}
+
+// SCALAR (the recurrence of designs with one decay a_t and one input scale b_t per head and token,
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T,  o_t = S_t^T q_t):
+// `alpha` is then float [T, heads, 2] = (a_t, b_t); q and k rows have `qk_stride` floats and hold qk_heads heads, head h
+// reading head h / (heads / qk_heads) (several heads may share one q and k); with `nstate` the state has one more
+// column, n_t = a_t n_(t-1) + b_t k_t (the column whose v is 1), kept as [slots, heads, dim], and its product with q goes
+// to qn [T, heads].
 // The tokens of a stage are copied into shared memory asynchronously while the stage before is computed (two buffers):
 // with one sequence there are few blocks, and a block that waited for its loads between stages spent half its time so.
-template <typename T, int COLS, int ROWS>
+template <typename T, int COLS, int ROWS, bool SCALAR>
 __global__ void __launch_bounds__(512)
 gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                 const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
-                const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
+                const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec,
+                int qk_heads, int qk_stride, float* __restrict__ nstate, float* __restrict__ qn) {
     extern __shared__ __align__(16) float sh[];
     constexpr int SPW = 32 / COLS;                    // row slices side by side in a warp
     const int slices = (blockDim.x >> 5) * SPW;
@@ -87,7 +114,8 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     float* qs = sh;                                   // q, k, alpha [2][GL_TOK][dimP] each
     float* ks = qs + 2 * buf;
     float* as = ks + 2 * buf;
-    float* vs = as + 2 * buf;                         // v [2][GL_TOK][COLS]
+    const int abuf = SCALAR ? 2 * GL_TOK : buf;       // one (a, b) pair a token instead of a decay per row
+    float* vs = as + 2 * abuf;                        // v [2][GL_TOK][COLS]
     constexpr int PER = ROWS / GL_SLICE;              // slices of GL_SLICE rows in a thread's rows
     const int n_sl = slices * PER;
     float* part = vs + 2 * GL_TOK * COLS;             // the sums of the slices of GL_SLICE rows [GL_TOK][n_sl][COLS]
@@ -98,17 +126,23 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     const int j = j0 + col, i0 = slice * ROWS;
     const int row0 = cu_q[b], row1 = cu_q[b + 1];
     const int slot = seq_slot[b];
-    const int width = heads * dim;
+    const int hq = SCALAR ? h / (heads / qk_heads) : h;
+    const int width = SCALAR ? qk_stride : heads * dim;
     float* S = state + ((size_t)slot * heads + h) * dim * vdim;
+    const bool has_n = SCALAR && nstate != nullptr;
+    const bool ncol = has_n && j == vdim;             // this thread's column is the normaliser's
+    float* Nn = has_n ? nstate + ((size_t)slot * heads + h) * dim : nullptr;
     // the padding rows never change: zero once, in both buffers
     for (int idx = threadIdx.x; idx < 2 * GL_TOK * (dimP - dim); idx += blockDim.x) {
         const int tt = idx / (dimP - dim), i = dim + idx - tt * (dimP - dim);
-        qs[tt * dimP + i] = 0.f; ks[tt * dimP + i] = 0.f; as[tt * dimP + i] = 0.f;
+        qs[tt * dimP + i] = 0.f; ks[tt * dimP + i] = 0.f;
+        if (!SCALAR) as[tt * dimP + i] = 0.f;
     }
     pdl_wait();
     float s[ROWS];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
+    for (int r = 0; r < ROWS; ++r)
+        s[r] = i0 + r < dim ? (j < vdim ? S[(size_t)(i0 + r) * vdim + j] : (ncol ? Nn[i0 + r] : 0.f)) : 0.f;
 
     // asynchronous copies of q, k, alpha of the stage that starts at token t0 into buffer p; the caller commits
     auto fetch = [&](int t0, int p) {
@@ -117,24 +151,30 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             const int d4 = dim >> 2;
             for (int idx = threadIdx.x; idx < cnt * d4; idx += blockDim.x) {
                 const int tt = idx / d4, i = (idx - tt * d4) << 2;
-                const size_t g = (size_t)(t0 + tt) * width + h * dim + i;
+                const size_t g = (size_t)(t0 + tt) * width + hq * dim + i;
                 const int d = p * buf + tt * dimP + i;
-                gl_copy16(qs + d, q + g); gl_copy16(ks + d, k + g); gl_copy16(as + d, alpha + g);
+                gl_copy16(qs + d, q + g); gl_copy16(ks + d, k + g);
+                if (!SCALAR) gl_copy16(as + d, alpha + g);
             }
         } else {
             for (int idx = threadIdx.x; idx < cnt * dim; idx += blockDim.x) {
                 const int tt = idx / dim, i = idx - tt * dim;
-                const size_t g = (size_t)(t0 + tt) * width + h * dim + i;
+                const size_t g = (size_t)(t0 + tt) * width + hq * dim + i;
                 const int d = p * buf + tt * dimP + i;
-                gl_copy4(qs + d, q + g); gl_copy4(ks + d, k + g); gl_copy4(as + d, alpha + g);
+                gl_copy4(qs + d, q + g); gl_copy4(ks + d, k + g);
+                if (!SCALAR) gl_copy4(as + d, alpha + g);
             }
         }
+        if (SCALAR)
+            for (int idx = threadIdx.x; idx < cnt * 2; idx += blockDim.x)
+                gl_copy4(as + p * abuf + idx, alpha + ((size_t)(t0 + (idx >> 1)) * heads + h) * 2 + (idx & 1));
     };
     // v of a stage: GL_TOK * COLS values, up to sixteen per thread (a block has at least 32 threads), through registers
     auto v_value = [&](int t0, int idx) -> float {
         const int cnt = min(GL_TOK, row1 - t0);
         const int tt = idx / COLS, c = idx % COLS;
-        return (tt < cnt && j0 + c < vdim) ? Cvt<T>::to_f32(v[(size_t)(t0 + tt) * v_stride + h * vdim + j0 + c]) : 0.f;
+        if (tt < cnt && j0 + c < vdim) return Cvt<T>::to_f32(v[(size_t)(t0 + tt) * v_stride + h * vdim + j0 + c]);
+        return (has_n && tt < cnt && j0 + c == vdim) ? 1.f : 0.f;
     };
     if (row0 < row1) {
         fetch(row0, 0);
@@ -159,12 +199,15 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         __syncthreads();
         const float* qb = qs + p * buf;
         const float* kb = ks + p * buf;
-        const float* ab = as + p * buf;
+        const float* ab = as + p * abuf;
         const float* vb = vs + p * GL_TOK * COLS;
 #pragma unroll 2
         for (int tt = 0; tt < cnt; ++tt) {
             float sums[PER];
-            gl_token<ROWS>(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col], sums);
+            if constexpr (SCALAR)
+                gl_token_scalar<ROWS>(s, ab[2 * tt], kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col] * ab[2 * tt + 1], sums);
+            else
+                gl_token<ROWS>(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col], sums);
 #pragma unroll
             for (int u = 0; u < PER; ++u) part[(tt * n_sl + slice * PER + u) * COLS + col] = sums[u];
         }
@@ -174,6 +217,7 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             float sum = 0.f;
             for (int w = 0; w < n_sl; ++w) sum += part[(tt * n_sl + w) * COLS + c];
             if (j0 + c < vdim) o[(size_t)(t0 + tt) * heads * vdim + h * vdim + j0 + c] = sum;
+            else if (has_n && qn != nullptr && j0 + c == vdim) qn[(size_t)(t0 + tt) * heads + h] = sum;
         }
         if (more) {
 #pragma unroll
@@ -188,17 +232,22 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
             if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
+    } else if (ncol) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if (i0 + r < dim) Nn[i0 + r] = s[r];
     }
 }
 
 // One token per sequence (decoding): the same arithmetic without the staging.  grid (sequence, head, ceil(vdim / 32)),
 // a warp per ROWS rows as above; a thread reads its rows' q, k and alpha straight from global memory (16 bytes at a
 // time where aligned, the same address for all lanes of a warp) and its state elements once, and writes them once.
-template <typename T, int ROWS>
+template <typename T, int ROWS, bool SCALAR>
 __global__ void __launch_bounds__(512)
 gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                   const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
-                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
+                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec,
+                  int qk_heads, int qk_stride, float* __restrict__ nstate, float* __restrict__ qn) {
     constexpr int PER = ROWS / GL_SLICE;
     __shared__ float part[32 * 32];                   // up to 256 / GL_SLICE slices
     pdl_trigger();
@@ -207,19 +256,32 @@ gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int j = j0 + lane, i0 = warp * ROWS;
     const int t = cu_q[b];
     float* S = state + ((size_t)seq_slot[b] * heads + h) * dim * vdim;
+    const bool ncol = SCALAR && nstate != nullptr && j == vdim;
+    float* Nn = ncol ? nstate + ((size_t)seq_slot[b] * heads + h) * dim : nullptr;
     pdl_wait();
     float s[ROWS];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
-    const size_t g = (size_t)t * heads * dim + (size_t)h * dim + i0;
+    for (int r = 0; r < ROWS; ++r)
+        s[r] = i0 + r < dim ? (j < vdim ? S[(size_t)(i0 + r) * vdim + j] : (ncol ? Nn[i0 + r] : 0.f)) : 0.f;
+    const size_t g = SCALAR ? (size_t)t * qk_stride + (size_t)(h / (heads / qk_heads)) * dim + i0
+                            : (size_t)t * heads * dim + (size_t)h * dim + i0;
     float a[ROWS], kk[ROWS], qq[ROWS];
+    float bt = 1.f;
+    if (SCALAR) {
+        const float at = alpha[((size_t)t * heads + h) * 2];
+        bt = alpha[((size_t)t * heads + h) * 2 + 1];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) a[r] = at;
+    }
     if (vec && i0 + ROWS <= dim) {
 #pragma unroll
         for (int r = 0; r < ROWS; r += 4) {
-            const float4 a4 = *reinterpret_cast<const float4*>(alpha + g + r);
+            if (!SCALAR) {
+                const float4 a4 = *reinterpret_cast<const float4*>(alpha + g + r);
+                a[r] = a4.x; a[r + 1] = a4.y; a[r + 2] = a4.z; a[r + 3] = a4.w;
+            }
             const float4 k4 = *reinterpret_cast<const float4*>(k + g + r);
             const float4 q4 = *reinterpret_cast<const float4*>(q + g + r);
-            a[r] = a4.x; a[r + 1] = a4.y; a[r + 2] = a4.z; a[r + 3] = a4.w;
             kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
             qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
         }
@@ -227,10 +289,11 @@ gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             const bool in = i0 + r < dim;
-            a[r] = in ? alpha[g + r] : 0.f; kk[r] = in ? k[g + r] : 0.f; qq[r] = in ? q[g + r] : 0.f;
+            if (!SCALAR) a[r] = in ? alpha[g + r] : 0.f;
+            kk[r] = in ? k[g + r] : 0.f; qq[r] = in ? q[g + r] : 0.f;
         }
     }
-    const float vj = j < vdim ? Cvt<T>::to_f32(v[(size_t)t * v_stride + h * vdim + j]) : 0.f;
+    const float vj = (j < vdim ? Cvt<T>::to_f32(v[(size_t)t * v_stride + h * vdim + j]) : (ncol ? 1.f : 0.f)) * bt;
 #pragma unroll
     for (int u = 0; u < PER; ++u) {                   // the same operations in the same order as gl_token
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -245,66 +308,82 @@ gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
             if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
+    } else if (ncol) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if (i0 + r < dim) Nn[i0 + r] = s[r];
     }
     __syncthreads();
-    if (warp == 0 && j < vdim) {
+    if (warp == 0 && (j < vdim || ncol)) {
         float sum = 0.f;
         for (int w = 0; w < warps * PER; ++w) sum += part[w * 32 + lane];
-        o[(size_t)t * heads * vdim + h * vdim + j] = sum;
+        if (j < vdim) o[(size_t)t * heads * vdim + h * vdim + j] = sum;
+        else if (qn != nullptr) qn[(size_t)t * heads + h] = sum;
     }
 }
 
-template <typename T, int COLS, int ROWS>
+// What the scalar form adds to a launch (all unused by the form with a decay per key channel).
+struct ScalarArgs {
+    int qk_heads, qk_stride;
+    float* nstate;
+    float* qn;
+};
+
+template <typename T, int COLS, int ROWS, bool SCALAR>
 static int launch_scan_cols(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                             float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int vec,
-                            cudaStream_t st) {
+                            ScalarArgs x, cudaStream_t st) {
     constexpr int SPW = 32 / COLS;
     const int slices = ((dim + ROWS - 1) / ROWS + SPW - 1) / SPW * SPW;
     const int warps = slices / SPW;
-    const int gz = (vdim + COLS - 1) / COLS;
+    const int gz = (vdim + (x.nstate != nullptr ? 1 : 0) + COLS - 1) / COLS;
     if (gz > 65535) return RF_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(6 * GL_TOK * slices * ROWS + 2 * GL_TOK * COLS + GL_TOK * slices * (ROWS / GL_SLICE) * COLS) * sizeof(float);
+    const size_t smem = (size_t)((SCALAR ? 4 : 6) * GL_TOK * slices * ROWS + (SCALAR ? 4 * GL_TOK : 0) + 2 * GL_TOK * COLS +
+                                 GL_TOK * slices * (ROWS / GL_SLICE) * COLS) * sizeof(float);
     static size_t configured = 48 * 1024;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, COLS, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, COLS, ROWS, SCALAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    rf_launch(gla_scan_kernel<T, COLS, ROWS>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
-              v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+    rf_launch(gla_scan_kernel<T, COLS, ROWS, SCALAR>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
+              v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec, x.qk_heads, x.qk_stride, x.nstate, x.qn);
     RF_LAUNCH_CHECK();
     return 0;
 }
 
 // ROWS: the rows of the state in a thread's registers (see launch_scan).
-template <typename T, int ROWS>
+template <typename T, int ROWS, bool SCALAR>
 static int launch_scan_rows(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                             float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
-                            int sms, cudaStream_t st) {
+                            int sms, ScalarArgs x, cudaStream_t st) {
     const int warps = (dim + ROWS - 1) / ROWS;
-    const int gz = (vdim + 31) / 32;
+    const int cols = vdim + (x.nstate != nullptr ? 1 : 0);
+    const int gz = (cols + 31) / 32;
     if (warps > 16 || gz > 65535) return RF_ERR_UNSUPPORTED;
     // rows of q, k, alpha are copied 16 bytes at a time where a head's slice of every token starts on such a boundary
-    const int vec = dim % 4 == 0 && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
-                                       reinterpret_cast<uintptr_t>(alpha)) & 15);
+    const int vec = dim % 4 == 0 && (!SCALAR || x.qk_stride % 4 == 0) &&
+                    !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                       (SCALAR ? 0 : reinterpret_cast<uintptr_t>(alpha))) & 15);
     if (one_token) {
-        rf_launch(gla_decode_kernel<T, ROWS>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
-                  v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+        rf_launch(gla_decode_kernel<T, ROWS, SCALAR>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
+                  v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec, x.qk_heads, x.qk_stride, x.nstate, x.qn);
         RF_LAUNCH_CHECK();
         return 0;
     }
     if (sms <= 0) sms = 148;
     if ((long long)B * heads * gz < sms)              // few blocks: narrower ones, twice as many
-        return launch_scan_cols<T, 16, ROWS>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
-    return launch_scan_cols<T, 32, ROWS>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
+        return launch_scan_cols<T, 16, ROWS, SCALAR>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, x, st);
+    return launch_scan_cols<T, 32, ROWS, SCALAR>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, x, st);
 }
 
-template <typename T>
+template <typename T, bool SCALAR>
 static int launch_scan(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                        float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
-                       int sms, cudaStream_t st) {
+                       int sms, ScalarArgs x, cudaStream_t st) {
     if (B <= 0) return 0;
     if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535) return RF_ERR_UNSUPPORTED;
+    if (SCALAR && (x.qk_heads <= 0 || heads % x.qk_heads || x.qk_stride < x.qk_heads * dim)) return RF_ERR_BAD_ARG;
     // Eight rows a thread (twice the warps, half the chain of each) while the step has too few (sequence, head) pairs to
     // fill the SMs twice over, sixteen beyond (fewer instructions per product) and for more than 128 key channels (a block
     // has at most sixteen warps).  Measured on 16 heads of 128 x 128, 2,048 tokens a sequence: one sequence 533 us with
@@ -312,8 +391,8 @@ static int launch_scan(const float* q, const float* k, const float* alpha, const
     // rows in both, so the choice changes no bit.
     if (sms <= 0) sms = 148;
     if (dim <= 128 && (long long)B * heads * ((vdim + 31) / 32) < 2LL * sms)
-        return launch_scan_rows<T, 8>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
-    return launch_scan_rows<T, 16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
+        return launch_scan_rows<T, 8, SCALAR>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st);
+    return launch_scan_rows<T, 16, SCALAR>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st);
 }
 
 template <typename T>
@@ -343,7 +422,19 @@ int rf_gla_prepare(int dtype, const void* src, int row_stride, int q_col, int k_
 int rf_gla_scan(int dtype, const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                 float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token, int sms,
                 cudaStream_t st) {
-    return dtype == 0 ? launch_scan<float>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st)
-                      : launch_scan<__nv_bfloat16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
+    const ScalarArgs none = {heads, heads * dim, nullptr, nullptr};
+    return dtype == 0 ? launch_scan<float, false>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, none, st)
+                      : launch_scan<__nv_bfloat16, false>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, none, st);
+}
+// The recurrence with one decay and one input scale per head and token: S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t.
+// q, k float rows of qk_stride floats that hold qk_heads heads of dim (head h reads head h / (heads / qk_heads));
+// ab float [T, heads, 2] = (a_t, b_t); v [T, v_stride] of dtype (heads * vdim columns); state float [slots, heads, dim, vdim].
+// nstate (may be null) float [slots, heads, dim]: n_t = a_t n_(t-1) + b_t k_t, and qn float [T, heads] receives n_t . q_t.
+int rf_gated_scan(int dtype, const float* q, const float* k, int qk_heads, int qk_stride, const float* ab, const void* v,
+                  int v_stride, float* state, float* nstate, float* o, float* qn, const int* cu_q, const int* seq_slot, int B,
+                  int heads, int dim, int vdim, int one_token, int sms, cudaStream_t st) {
+    const ScalarArgs x = {qk_heads, qk_stride, nstate, qn};
+    return dtype == 0 ? launch_scan<float, true>(q, k, ab, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st)
+                      : launch_scan<__nv_bfloat16, true>(q, k, ab, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st);
 }
 }

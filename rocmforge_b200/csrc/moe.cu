@@ -3,7 +3,8 @@
 //
 //   moe_route     per token: the `top` largest of E router logits (32-bit; of equal logits the lower index), and
 //                 their weights: the softmax over the chosen logits only (scoring 0), or each chosen logit's own
-//                 sigmoid, not renormalised (scoring 1)
+//                 sigmoid, not renormalised (scoring 1), or each chosen logit's share of the softmax over all E
+//                 logits, not renormalised (scoring 2)
 //   moe_sort      counting sort of the T*top (token, choice) pairs by expert: perm[sorted row] = pair,
 //                 inv[pair] = sorted row, and the table of row tiles for the grouped product
 //                 (tiles[0] = number of tiles, then (expert, first row, end row) per tile; a tile never spans experts)
@@ -35,6 +36,16 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
         }
         chosen[k] = best;
         val[k] = bv;
+    }
+    if (scoring == 2) {                              // the chosen experts' shares of the softmax over ALL experts
+        float largest = -INFINITY, sum = 0.f;
+        for (int e = 0; e < E; ++e) largest = fmaxf(largest, z[e]);
+        for (int e = 0; e < E; ++e) sum += expf(z[e] - largest);
+        for (int k = 0; k < top; ++k) {
+            idx[(size_t)t * top + k] = chosen[k];
+            w[(size_t)t * top + k] = expf(val[k] - largest) / sum;
+        }
+        return;
     }
     if (scoring == 1) {
         for (int k = 0; k < top; ++k) {
@@ -133,7 +144,7 @@ int rf_moe_gather(const void* x, long long x_stride_bytes, const int* perm, int 
 static int route(const float* logits, int E, int top, int* idx, float* w, int T_, int scoring, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > E) return RF_ERR_UNSUPPORTED;
-    if (scoring != 0 && scoring != 1) return RF_ERR_BAD_ARG;
+    if (scoring < 0 || scoring > 2) return RF_ERR_BAD_ARG;
     rf_launch(moe_route_kernel, dim3((T_ + 127) / 128), dim3(128), 0, st, logits, E, top, idx, w, T_, scoring);
     RF_LAUNCH_CHECK();
     return 0;
@@ -141,7 +152,7 @@ static int route(const float* logits, int E, int top, int* idx, float* w, int T_
 int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_, cudaStream_t st) {
     return route(logits, E, top, idx, w, T_, 0, st);
 }
-// scoring: 0 = softmax over the chosen logits, 1 = sigmoid of each chosen logit
+// scoring: 0 = softmax over the chosen logits, 1 = sigmoid of each chosen logit, 2 = share of the softmax over all logits
 int rf_moe_route_scored(const float* logits, int E, int top, int* idx, float* w, int T_, int scoring, cudaStream_t st) {
     return route(logits, E, top, idx, w, T_, scoring, st);
 }

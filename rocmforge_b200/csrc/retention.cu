@@ -125,7 +125,8 @@ retention_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, 
 template <typename T>
 __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
                                       T* __restrict__ out, int heads, int vdim, float eps, int T_,
-                                      const void* __restrict__ norm_w, int w_is_f32) {
+                                      const void* __restrict__ norm_w, int w_is_f32, int w_per_head, int sigmoid,
+                                      const float* __restrict__ qn, const float* __restrict__ mt) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -135,13 +136,16 @@ __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __re
         const long long t = w / heads;
         const int h = (int)(w - t * heads);
         const float* orow = o + (size_t)t * heads * vdim + (size_t)h * vdim;
+        // a denominator of the head: max(|n . q|, exp(-m)) + 1e-6, before the norm (designs with a normaliser state)
+        const float inv = qn != nullptr ? 1.f / (fmaxf(fabsf(qn[w]), expf(-mt[w])) + 1e-6f) : 1.f;
         float ss = 0.f;
-        for (int e = lane; e < vdim; e += 32) ss += orow[e] * orow[e];
+        for (int e = lane; e < vdim; e += 32) { const float x = orow[e] * inv; ss += x * x; }
         const float r = rsqrtf(warp_sum(ss) / (float)vdim + eps);
         for (int e = lane; e < vdim; e += 32) {
             const float g = Cvt<T>::to_f32(gate[(size_t)t * gate_stride + (size_t)h * vdim + e]);
-            const float wn = norm_w != nullptr ? load_vec(norm_w, w_is_f32, e) : 1.f;
-            out[(size_t)t * heads * vdim + (size_t)h * vdim + e] = Cvt<T>::from_f32(orow[e] * r * wn * (g / (1.f + expf(-g))));
+            const float wn = norm_w != nullptr ? load_vec(norm_w, w_is_f32, w_per_head ? h * vdim + e : e) : 1.f;
+            const float gv = sigmoid ? 1.f / (1.f + expf(-g)) : g / (1.f + expf(-g));
+            out[(size_t)t * heads * vdim + (size_t)h * vdim + e] = Cvt<T>::from_f32(orow[e] * inv * r * wn * gv);
         }
     }
 }
@@ -428,12 +432,14 @@ static int launch_scan(const float* q, const float* k, const void* v, int v_stri
 
 template <typename T>
 static int launch_gate(const float* o, const void* gate, int gate_stride, void* out, int heads, int vdim, float eps, int T_,
-                       cudaStream_t st, const void* w = nullptr, int w_is_f32 = 0) {
+                       cudaStream_t st, const void* w = nullptr, int w_is_f32 = 0, int w_per_head = 0, int sigmoid = 0,
+                       const float* qn = nullptr, const float* mt = nullptr) {
     const long long total = (long long)T_ * heads;
     if (total <= 0) return 0;
     const long long blocks = (total + 7) / 8;
     rf_launch(retention_gate_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st, o,
-              reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), heads, vdim, eps, T_, w, w_is_f32);
+              reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), heads, vdim, eps, T_, w, w_is_f32, w_per_head,
+              sigmoid, qn, mt);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -468,5 +474,15 @@ int rf_retention_gate_w(int dtype, const float* o, const void* gate, int gate_st
                         int T_, const void* w, int w_is_f32, cudaStream_t st) {
     return dtype == 0 ? launch_gate<float>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32)
                       : launch_gate<__nv_bfloat16>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32);
+}
+// The general form: the weight is [vdim] for all heads or (w_per_head) [heads * vdim]; the gate's function is silu or
+// (sigmoid) the sigmoid; with qn and mt (float [T, heads] each) every head is first divided by
+// max(|qn|, exp(-mt)) + 1e-6.
+int rf_retention_gate_x(int dtype, const float* o, const void* gate, int gate_stride, void* out, int heads, int vdim, float eps,
+                        int T_, const void* w, int w_is_f32, int w_per_head, int sigmoid, const float* qn, const float* mt,
+                        cudaStream_t st) {
+    if ((qn == nullptr) != (mt == nullptr)) return RF_ERR_BAD_ARG;
+    return dtype == 0 ? launch_gate<float>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32, w_per_head, sigmoid, qn, mt)
+                      : launch_gate<__nv_bfloat16>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32, w_per_head, sigmoid, qn, mt);
 }
 }

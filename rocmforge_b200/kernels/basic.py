@@ -82,15 +82,18 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float, row_scale: torch.T
     return out
 
 
-def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
-    """x * sigmoid(gate), element by element (32-bit inside); both [T, W] views with unit inner stride."""
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> torch.Tensor:
+    """x * sigmoid(gate), 32-bit inside; x [T, W] and gate [T, W / group] views with unit inner stride: column c of x is
+    gated by column c // group (``group`` 1: a gate per element; a head's size: one gate per head)."""
     need_cuda(x, gate)
-    need(x.dim() == 2 and gate.shape == x.shape and x.stride(1) == 1 and gate.stride(1) == 1 and x.dtype == gate.dtype,
-         "sigmoid_gate: x and gate must be [T, W] of one dtype")
+    need(x.dim() == 2 and group >= 1 and x.shape[1] % group == 0 and gate.shape == (x.shape[0], x.shape[1] // group)
+         and x.stride(1) == 1 and gate.stride(1) == 1 and x.dtype == gate.dtype,
+         "sigmoid_gate: x [T, W] and gate [T, W / group] must share a dtype")
     T, W = x.shape
     out = torch.empty((T, W), dtype=x.dtype, device=x.device)
-    f = _f("elementwise", "rf_sigmoid_gate", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
-    check(f(dtype_code(x.dtype), ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(out), T, W, stream()), "sigmoid_gate")
+    f = _f("elementwise", "rf_sigmoid_gate", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(out), T, W, int(group), stream()),
+          "sigmoid_gate")
     return out
 
 
@@ -265,9 +268,10 @@ def key_span(window: int | None, chunk: int | None = None) -> int:
 def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                       tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                       out: torch.Tensor | None = None, *, v_head_dim: int | None = None, softcap: float | None = None,
-                      slopes: torch.Tensor | None = None, chunk: int | None = None) -> torch.Tensor:
+                      slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
     """Attention of the T new tokens over the paged cache (their own keys included).  ``window`` / ``chunk``: see
-    ``key_span``.
+    ``key_span``.  ``keep_first``: with a window, the first ``keep_first`` positions of a sequence stay visible to every
+    later query as well (at their own positions).
 
     ``v_head_dim``: size of a value head where it differs from a key head's (the output is [T, heads * v_head_dim]);
     ``softcap``: scores become softcap * tanh(score / softcap); ``slopes`` (float32 [heads]): after the cap, a score is
@@ -283,15 +287,16 @@ def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
     if out is None:
         out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
     window = key_span(window, chunk)
-    if vd != head_dim or softcap or slopes is not None:
+    keep_first = int(keep_first or 0) if window > 0 else 0         # without a window every key is visible anyway
+    if vd != head_dim or softcap or slopes is not None or keep_first:
         need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
              "attention: slopes must be float32 [heads]")
         f = _f("attention_generic", "rf_attention_generic_ext", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-               c_void_p, c_int, c_int, c_void_p)
+               c_void_p, c_int, c_int, c_int, c_void_p)
         check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
                 ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
-                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), window, T, stream()),
+                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), window, keep_first, T, stream()),
               f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, v_head_dim={vd})")
         return out
     f = _f("attention_generic", "rf_attention_generic", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
@@ -631,13 +636,13 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
                        compute_dtype: torch.dtype | None = None, rot_dim: int = 0, interleaved: bool = False,
                        unit_norm_eps: float | None = None, q_norm_weight: torch.Tensor | None = None,
-                       k_norm_weight: torch.Tensor | None = None) -> torch.Tensor:
+                       k_norm_weight: torch.Tensor | None = None, magnitude: float = 1.0) -> torch.Tensor:
     """q | k | v rows on their way into the cache, for heads that are normed and for values of another size than keys.
 
     ``qkv`` is [T, heads*head_dim + kv_heads*head_dim + kv_heads*v_head_dim] in the compute dtype, or a float32 stack
     [S, T, ...] of partial sums.  With ``unit_norm_eps`` every query and key head is divided by its root mean square
     (x / sqrt(mean(x^2) + eps)) in 32-bit and multiplied by ``q_norm_weight`` / ``k_norm_weight`` ([head_dim], shared by
-    the heads) where given; then the first ``rot_dim`` elements turn (0: no rotation).  The rows may hold more columns
+    the heads) where given; then the first ``rot_dim`` elements turn (0: no rotation), sine and cosine times ``magnitude``.  The rows may hold more columns
     than q | k | v (a gate's, say); without ``write_kv`` only the q heads are read.
     Returns q [T, heads*head_dim] in the compute dtype; k and v go to their pages.
     """
@@ -667,12 +672,12 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
          "head_norm_kv_write: norm weights are [head_dim] vectors of one dtype and go with unit_norm_eps")
     f = _f("elementwise", "rf_head_norm_kv_write_w", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-           c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p)
+           c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p)
     check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(q_out), q_out.stride(0), n_heads, n_kv_heads, head_dim,
             v_head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
             ptr(k_pages), ptr(v_pages), int(write_kv), T, int(rot_dim), int(interleaved), int(unit_norm_eps is not None),
             float(unit_norm_eps or 0.0), ptr(q_norm_weight), ptr(k_norm_weight), int(bool(nws) and nws[0].dtype == torch.float32),
-            stream()), "head_norm_kv_write")
+            float(magnitude), stream()), "head_norm_kv_write")
     return q_out
 
 
@@ -767,20 +772,29 @@ def retention_chunked(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, de
 
 
 def retention_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float,
-                   weight: torch.Tensor | None = None) -> torch.Tensor:
-    """o / sqrt(mean(o^2) + eps) per head (times ``weight`` [vdim], one vector for all heads, if given), times silu(gate),
-    in the gate's dtype."""
+                   weight: torch.Tensor | None = None, *, gate_fn: str = "silu", denominator=None) -> torch.Tensor:
+    """o / sqrt(mean(o^2) + eps) per head, times ``weight`` if given ([vdim], one vector for all heads, or [heads*vdim]),
+    times silu(gate) (``gate_fn`` "sigmoid": sigmoid(gate)), in the gate's dtype.  ``denominator`` = (qn, m), float32
+    [T, heads] each: every head is first divided by max(|qn|, exp(-m)) + 1e-6."""
     need_cuda(o, gate, weight)
-    need(weight is None or (weight.shape == (vdim,) and weight.is_contiguous() and weight.dtype in (torch.float32, torch.bfloat16)),
-         "retention_gate: the norm's weight must be [vdim]")
+    need(gate_fn in ("silu", "sigmoid"), f"retention_gate: gate function {gate_fn!r} (silu, sigmoid)")
+    need(weight is None or (weight.shape in ((vdim,), (heads * vdim,)) and weight.is_contiguous()
+                            and weight.dtype in (torch.float32, torch.bfloat16)),
+         "retention_gate: the norm's weight must be [vdim] or [heads*vdim]")
     T = o.shape[0]
     need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * vdim), "retention_gate: bad o")
     need(gate.shape == (T, heads * vdim) and gate.stride(1) == 1, "retention_gate: gate must be [T, heads*vdim]")
+    qn, mt = denominator if denominator is not None else (None, None)
+    for d in (qn, mt):
+        need(d is None or (d.is_cuda and d.dtype == torch.float32 and d.shape == (T, heads) and d.is_contiguous()),
+             "retention_gate: the denominator's parts must be float32 [T, heads]")
     out = torch.empty((T, heads * vdim), dtype=gate.dtype, device=o.device)
-    f = _f("retention", "rf_retention_gate_w", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int,
-           c_void_p, c_int, c_void_p)
+    per_head = weight is not None and heads > 1 and weight.shape == (heads * vdim,)
+    f = _f("retention", "rf_retention_gate_x", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int,
+           c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p)
     check(f(dtype_code(gate.dtype), ptr(o), ptr(gate), gate.stride(0), ptr(out), heads, vdim, float(eps), T, ptr(weight),
-            int(weight is not None and weight.dtype == torch.float32), stream()), "retention_gate")
+            int(weight is not None and weight.dtype == torch.float32), int(per_head), int(gate_fn == "sigmoid"), ptr(qn),
+            ptr(mt), stream()), "retention_gate")
     return out
 
 
@@ -843,13 +857,14 @@ def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int) -> torch.Tensor:
     return out
 
 
-MOE_SCORINGS = {"softmax_of_chosen": 0, "sigmoid": 1}
+MOE_SCORINGS = {"softmax_of_chosen": 0, "sigmoid": 1, "softmax_of_all": 2}
 
 
 def moe_route(logits: torch.Tensor, top: int, scoring: str = "softmax_of_chosen"):
     """(experts int32 [T, top], weights float32 [T, top]): the ``top`` largest router logits of every token (of equal
     logits the lower index) and their weights: the softmax over those alone, or (``scoring`` "sigmoid") each one's
-    own sigmoid, not renormalised."""
+    own sigmoid, not renormalised, or ("softmax_of_all") each one's share of the softmax over all E logits, not
+    renormalised."""
     need(scoring in MOE_SCORINGS, f"moe_route: scoring {scoring!r} is not one of {sorted(MOE_SCORINGS)}")
     need_cuda(logits)
     need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "moe_route: logits must be float32 [T, E]")
@@ -901,4 +916,205 @@ def moe_combine(y: torch.Tensor, inv: torch.Tensor, w: torch.Tensor | None, top:
     out = torch.empty((T, H), dtype=torch.float32, device=y.device)
     f = _f("moe", "rf_moe_combine", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p)
     check(f(ptr(y), ptr(inv), ptr(w), ptr(out), top, H, T, stream()), "moe_combine")
+    return out
+
+
+# ---------------------------------------------------------------- Dynamic Tanh and the scaled residual update (csrc/elementwise.cu)
+
+def dyt_rows(h: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, compute_dtype: torch.dtype,
+             rows: torch.Tensor | None = None) -> torch.Tensor:
+    """y = tanh(alpha h) * weight + bias in the compute dtype, of all rows of the float32 stream ``h`` [T, H] or of those
+    that ``rows`` (int32) lists; alpha (one number), weight and bias [H] are float32."""
+    need_cuda(h, alpha, weight, bias, rows)
+    need(h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous(), "dyt_rows: h must be contiguous float32 [T, H]")
+    T, H = h.shape
+    need(all(v.dtype == torch.float32 and v.is_contiguous() for v in (alpha, weight, bias)) and alpha.numel() == 1
+         and weight.shape == (H,) and bias.shape == (H,), "dyt_rows: alpha [1], weight [H] and bias [H] must be float32")
+    need(rows is None or rows.dtype == torch.int32, "dyt_rows: rows must be int32")
+    R = T if rows is None else rows.numel()
+    y = torch.empty((R, H), dtype=compute_dtype, device=h.device)
+    f = _f("elementwise", "rf_dyt_rows", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+           c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(rows), ptr(alpha), ptr(weight), ptr(bias), ptr(y), R, H, stream()),
+          f"dyt_rows (H={H})")
+    return y
+
+
+def scaled_add(h: torch.Tensor, addends, mult: float, compute_dtype: torch.dtype, *, eps: float = 0.0,
+               next_dyt=None) -> torch.Tensor | None:
+    """The residual update of a block that scales its sub-layers' outputs, in 32-bit and one pass over the rows:
+
+        m = a0 (+ a1)                             for addends == [(a0, None)] or [(a0, None), (a1, None)]
+        m = (rms(a0) * w0 + rms(a1) * w1) / 2     for addends == [(a0, w0), (a1, w1)], rms(x) = x / sqrt(mean(x^2) + eps)
+        h += mult * m
+        returns tanh(alpha h) * w + b in the compute dtype if ``next_dyt`` = (alpha, w, b) (float32) is given, else None
+
+    An addend is float32 [T, H] or a stack [S, T, H] of a K-split product's partial sums, added here in index order.
+    """
+    need(len(addends) in (1, 2), "scaled_add: one or two addends")
+    a0, w0 = addends[0]
+    a1, w1 = addends[1] if len(addends) == 2 else (None, None)
+    need((w0 is None) == (w1 is None) or a1 is None, "scaled_add: both addends are normed with a weight, or neither")
+    need(not (a1 is None and w0 is not None), "scaled_add: one addend comes without a weight")
+    vecs = [v for v in (w0, w1) if v is not None]
+    nd = list(next_dyt) if next_dyt is not None else []
+    need_cuda(h, a0, a1, *vecs, *nd)
+    T, H = h.shape
+    need(h.dtype == torch.float32 and h.is_contiguous(), "scaled_add: h must be contiguous float32 [T, H]")
+    for a in (a0, a1):
+        need(a is None or (a.dtype == torch.float32 and tuple(a.shape[-2:]) == (T, H) and a.dim() in (2, 3) and a.is_contiguous()),
+             "scaled_add: an addend must be contiguous float32 [T, H] or [S, T, H]")
+    need(all(v.shape == (H,) and v.is_contiguous() and v.dtype == vecs[0].dtype for v in vecs)
+         and (not vecs or vecs[0].dtype in (torch.float32, torch.bfloat16)), "scaled_add: the weights must be [H] of one dtype")
+    if nd:
+        need(len(nd) == 3 and all(v.dtype == torch.float32 and v.is_contiguous() for v in nd) and nd[0].numel() == 1
+             and nd[1].shape == (H,) and nd[2].shape == (H,), "scaled_add: the next norm is (alpha [1], weight [H], bias [H]) in float32")
+    n0 = a0.shape[0] if a0.dim() == 3 else 1
+    n1 = (a1.shape[0] if a1.dim() == 3 else 1) if a1 is not None else 0
+    y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if nd else None
+    f = _f("elementwise", "rf_scaled_add", c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+           c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), n0, ptr(w0), ptr(a1), n1, ptr(w1),
+            int(bool(vecs) and vecs[0].dtype == torch.float32), float(eps), float(mult), ptr(nd[0] if nd else None),
+            ptr(nd[1] if nd else None), ptr(nd[2] if nd else None), ptr(y), T, H, stream()), f"scaled_add (H={H})")
+    return y
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), in place, float32."""
+    need_cuda(x)
+    need(x.dtype == torch.float32 and x.is_contiguous(), "softcap: a contiguous float32 tensor")
+    f = _f("elementwise", "rf_softcap", c_void_p, c_ll, c_float, c_void_p)
+    check(f(ptr(x), x.numel(), float(cap), stream()), "softcap")
+    return x
+
+
+# ---------------------------------------------------------------- recurrences with one decay per head and token (csrc/gla.cu)
+
+def gated_scan(q: torch.Tensor, k: torch.Tensor, ab: torch.Tensor, v: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+               seq_slot: torch.Tensor, heads: int, dim: int, vdim: int, *, qk_heads: int | None = None,
+               nstate: torch.Tensor | None = None, one_token: bool = False):
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t per head, token by token for every sequence of the step.
+
+    ``q``, ``k``: float32 [T, >= qk_heads*dim] views (rows may be strided; both with the same row stride) that hold
+    ``qk_heads`` heads of ``dim``; head h reads head h // (heads / qk_heads).  ``ab`` float32 [T, heads, 2] = (a_t, b_t).
+    ``v`` [T, heads*vdim] view of float32 or bfloat16.  ``state`` float32 [slots, heads, dim, vdim], read at the step's
+    start and left as after its last token.  With ``nstate`` (float32 [slots, heads, dim]) the normaliser
+    n_t = a_t n_(t-1) + b_t k_t is carried along and the second result is n_t . q_t, float32 [T, heads].
+    Returns (o float32 [T, heads*vdim], qn or None)."""
+    need_cuda(q, k, ab, v, state, cu_q, seq_slot, nstate)
+    T = ab.shape[0]
+    qk_heads = heads if qk_heads is None else int(qk_heads)
+    need(heads % qk_heads == 0, "gated_scan: the heads must share q and k heads evenly")
+    for x in (q, k):
+        need(x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] == T and x.shape[1] >= qk_heads * dim and x.stride(1) == 1
+             and x.stride(0) == q.stride(0), "gated_scan: q and k must be float32 [T, >= qk_heads*dim] with one row stride")
+    need(ab.dtype == torch.float32 and ab.is_contiguous() and ab.shape == (T, heads, 2), "gated_scan: ab must be float32 [T, heads, 2]")
+    need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "gated_scan: v must be [T, heads*vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+         "gated_scan: state must be float32 [slots, heads, dim, vdim]")
+    need(nstate is None or (nstate.dtype == torch.float32 and nstate.is_contiguous() and tuple(nstate.shape[1:]) == (heads, dim)),
+         "gated_scan: the normaliser's state must be float32 [slots, heads, dim]")
+    B = seq_slot.shape[0]
+    need(not one_token or T == B, "gated_scan: one_token means one token for every sequence")
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=ab.device)
+    qn = torch.empty((T, heads), dtype=torch.float32, device=ab.device) if nstate is not None else None
+    f = _f("gla", "rf_gated_scan", c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(v.dtype), ptr(q), ptr(k), qk_heads, q.stride(0), ptr(ab), ptr(v), v.stride(0), ptr(state), ptr(nstate),
+            ptr(o), ptr(qn), ptr(cu_q), ptr(seq_slot), B, heads, dim, vdim, int(one_token), device_sm_count(ab.device), stream()),
+          f"gated_scan (heads={heads}, dim={dim}, vdim={vdim})")
+    return o, qn
+
+
+# ---------------------------------------------------------------- matrix memory (csrc/mlstm.cu)
+
+def mlstm_prepare(proj: torch.Tensor, q_col: int, k_col: int, width: int, q_scale: float) -> torch.Tensor:
+    """float32 [2, T, width]: q of the projection's rows (columns q_col..) times ``q_scale``, and k (columns k_col..)."""
+    need_cuda(proj)
+    need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_col, k_col) + width <= proj.shape[1],
+         "mlstm_prepare: the projection must be [T, columns] and hold q and k")
+    T = proj.shape[0]
+    qk = torch.empty((2, T, width), dtype=torch.float32, device=proj.device)
+    f = _f("mlstm", "rf_mlstm_prepare", c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p)
+    check(f(dtype_code(proj.dtype), ptr(proj), proj.stride(0), q_col, k_col, ptr(qk), width, float(q_scale), T, stream()),
+          "mlstm_prepare")
+    return qk
+
+
+def mlstm_gates(z: torch.Tensor, mstate: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor, heads: int, cap: float,
+                max_new: int):
+    """The gates' chain of the matrix memory.  ``z`` float32 [T, 2*heads]: the input gate's pre-activations (bias added),
+    then the forget gate's.  li = cap tanh(zi / cap), lf = log sigmoid(cap tanh(zf / cap)) (cap <= 0: not capped),
+    m_t = max(lf + m_(t-1), li) from ``mstate`` float32 [slots, heads] (updated), a_t = exp(lf + m_(t-1) - m_t),
+    b_t = exp(li - m_t).  Returns (ab float32 [T, heads, 2], m float32 [T, heads])."""
+    need_cuda(z, mstate, cu_q, seq_slot)
+    T = z.shape[0]
+    need(z.dtype == torch.float32 and z.is_contiguous() and z.shape == (T, 2 * heads), "mlstm_gates: z must be float32 [T, 2*heads]")
+    need(mstate.dtype == torch.float32 and mstate.is_contiguous() and tuple(mstate.shape[1:]) == (heads,),
+         "mlstm_gates: the maximum's state must be float32 [slots, heads]")
+    ab = torch.empty((T, heads, 2), dtype=torch.float32, device=z.device)
+    mt = torch.empty((T, heads), dtype=torch.float32, device=z.device)
+    f = _f("mlstm", "rf_mlstm_gates", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+           c_void_p)
+    check(f(ptr(z), ptr(ab), ptr(mt), ptr(mstate), ptr(cu_q), ptr(seq_slot), seq_slot.shape[0], heads, float(cap or 0.0),
+            int(max_new), stream()), "mlstm_gates")
+    return ab, mt
+
+
+# ---------------------------------------------------------------- state-space mixer (csrc/mamba2.cu)
+
+def conv_silu(src: torch.Tensor, col0: int, channels: int, state: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+              tok_seq: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor) -> torch.Tensor:
+    """silu of a causal convolution per channel over the last ``taps`` inputs: ``src`` [T, columns], the channels from
+    column ``col0`` on; ``weight`` [channels, taps] (the last column weighs the current token) and ``bias`` [channels] of
+    one dtype; ``state`` float32 [slots, taps-1, channels] holds every sequence's inputs before the step (zeros at its
+    start) and is replaced by the step's last inputs.  Returns float32 [T, channels]."""
+    need_cuda(src, state, weight, bias, tok_seq, cu_q, seq_slot)
+    T = src.shape[0]
+    need(src.dim() == 2 and src.stride(1) == 1 and col0 + channels <= src.shape[1], "conv_silu: src must be [T, >= col0 + channels]")
+    taps = weight.shape[1]
+    need(weight.shape == (channels, taps) and bias.shape == (channels,) and weight.dtype == bias.dtype and weight.is_contiguous()
+         and bias.is_contiguous() and weight.dtype in (torch.float32, torch.bfloat16), "conv_silu: weight [channels, taps], bias [channels]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, channels),
+         "conv_silu: state must be float32 [slots, taps-1, channels]")
+    out = torch.empty((T, channels), dtype=torch.float32, device=src.device)
+    f = _f("mamba2", "rf_conv_silu", c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(src.dtype), ptr(src), src.stride(0), col0, ptr(state), ptr(weight), ptr(bias),
+            int(weight.dtype == torch.float32), ptr(out), ptr(tok_seq), ptr(cu_q), ptr(seq_slot), T, seq_slot.shape[0], channels,
+            taps, stream()), f"conv_silu (channels={channels}, taps={taps})")
+    return out
+
+
+def mamba_gates(z: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor) -> torch.Tensor:
+    """float32 [T, heads, 2] = (exp(-exp(a_log) dt), dt) with dt = softplus(z + dt_bias); z float32 [T, heads]."""
+    need_cuda(z, dt_bias, a_log)
+    T, heads = z.shape
+    need(z.dtype == torch.float32 and z.is_contiguous(), "mamba_gates: z must be contiguous float32 [T, heads]")
+    need(dt_bias.shape == (heads,) and a_log.shape == (heads,) and dt_bias.dtype == a_log.dtype and dt_bias.is_contiguous()
+         and a_log.is_contiguous() and a_log.dtype in (torch.float32, torch.bfloat16), "mamba_gates: dt_bias and a_log are [heads] of one dtype")
+    ab = torch.empty((T, heads, 2), dtype=torch.float32, device=z.device)
+    f = _f("mamba2", "rf_mamba_gates", c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
+    check(f(ptr(z), ptr(dt_bias), ptr(a_log), int(a_log.dtype == torch.float32), ptr(ab), T, heads, stream()), "mamba_gates")
+    return ab
+
+
+def mamba_finish(y: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, skip: torch.Tensor, norm_w: torch.Tensor, parts: int,
+                 vdim: int, eps: float) -> torch.Tensor:
+    """(y + skip[head] x) * silu(gate), each of the ``parts`` equal parts of a row divided by its own root mean square,
+    times ``norm_w``; y float32 [T, inner], x a float32 [T, inner] view, gate a [T, inner] view of the compute dtype (the
+    result's), skip [inner / vdim] and norm_w [inner] of one dtype."""
+    need_cuda(y, x, gate, skip, norm_w)
+    T, inner = y.shape
+    need(y.dtype == torch.float32 and y.is_contiguous() and x.dtype == torch.float32 and x.shape == (T, inner) and x.stride(1) == 1
+         and gate.shape == (T, inner) and gate.stride(1) == 1, "mamba_finish: y, x float32 [T, inner], gate [T, inner]")
+    need(inner % parts == 0 and inner % vdim == 0 and skip.shape == (inner // vdim,) and norm_w.shape == (inner,)
+         and skip.dtype == norm_w.dtype and skip.is_contiguous() and norm_w.is_contiguous()
+         and skip.dtype in (torch.float32, torch.bfloat16), "mamba_finish: skip [heads] and norm_w [inner] of one dtype")
+    out = torch.empty((T, inner), dtype=gate.dtype, device=y.device)
+    f = _f("mamba2", "rf_mamba_finish", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+           c_int, c_int, c_int, c_int, c_float, c_void_p)
+    check(f(dtype_code(gate.dtype), ptr(y), ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(skip), ptr(norm_w),
+            int(skip.dtype == torch.float32), ptr(out), T, inner, parts, vdim, float(eps), stream()), "mamba_finish")
     return out

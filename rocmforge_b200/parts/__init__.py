@@ -16,3 +16,9 @@ from .parallel import ParallelMixer
 from .offsets import PassOffsets
 from .gla import GatedLinearAttention
 from .embedding import LearnedPositions
+from .norm import DynamicTanh
+from .rope import YarnRope
+from .block import ScaledPreNormBlock
+from .mlp import SummedFeedForward
+from .mlstm import MatrixMemory
+from .mamba2 import StateSpaceDuality

@@ -38,7 +38,11 @@ class GQAAttention(Mixer):
     multiplied by sigmoid(W_g x) before the output projection; W_g reads the same input as q, k, v and is part of the same
     product), ``shares_kv`` (the mixer has no key and value tensors: the schedule lets it read another execution's
     cache, ``ScheduleEntry.kv_from``, with queries, mask and everything else of its own) and ``cache_keeps`` (what the
-    cache must keep when other mixers read it with masks of their own: "all", or None for this mixer's own mask).  Normed heads and values of another size go into the
+    cache must keep when other mixers read it with masks of their own: "all", or None for this mixer's own mask),
+    ``keep_first`` (with a window: the first ``keep_first`` positions of a sequence stay visible to every later query, at
+    their own positions; the cache keeps their pages) and ``gate`` "sigmoid_head" (one gate per head, W_g of ``heads``
+    rows: head h's output is multiplied by sigmoid(W_g x)_h).  A position encoding whose rotation carries a ``magnitude``
+    (sine and cosine times a factor) goes through the per-head writer as well.  Normed heads and values of another size go into the
     cache through the per-head writer; a cap and slopes are known to the generic attention and to the tcgen05 prompt
     attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
     on the same kernels as one without them.
@@ -51,7 +55,7 @@ class GQAAttention(Mixer):
                  scale: Optional[float] = None, v_head_dim: Optional[int] = None, qk_norm_eps: Optional[float] = None,
                  softcap: Optional[float] = None, distance_slopes=None, names: Optional[Dict[str, str]] = None,
                  qk_norm_weight: bool = False, chunk: Optional[int] = None, gate: Optional[str] = None,
-                 shares_kv: bool = False, cache_keeps: Optional[str] = None):
+                 shares_kv: bool = False, cache_keeps: Optional[str] = None, keep_first: int = 0):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
@@ -71,8 +75,13 @@ class GQAAttention(Mixer):
         self.chunk = int(chunk) if chunk else None
         if self.chunk is not None and window:
             raise ValueError("gqa_attention: a window or chunks, not both")
-        if gate not in (None, "sigmoid"):
-            raise ValueError(f"gqa_attention: gate {gate!r} has no kernel (sigmoid)")
+        if gate not in (None, "sigmoid", "sigmoid_head"):
+            raise ValueError(f"gqa_attention: gate {gate!r} has no kernel (sigmoid, sigmoid_head)")
+        self.keep_first = int(keep_first or 0)
+        if self.keep_first < 0 or (self.keep_first and self.chunk is not None):
+            raise ValueError("gqa_attention: keep_first is a number of first positions kept beside a window")
+        if not window:
+            self.keep_first = 0                           # without a window every earlier position is visible anyway
         if cache_keeps not in (None, "all"):
             raise ValueError(f"gqa_attention: cache_keeps {cache_keeps!r} (all, or None)")
         self.gate, self.shares_kv, self.cache_keeps = gate, bool(shares_kv), cache_keeps
@@ -84,9 +93,11 @@ class GQAAttention(Mixer):
         self.kv_size = n_kv_heads * head_dim
         self.v_size = n_kv_heads * self.v_head_dim
         self.o_in = n_heads * self.v_head_dim
+        self.gate_rows = n_heads if gate == "sigmoid_head" else self.o_in
+        self.magnitude = float(((position.rotation() if position is not None else None) or {}).get("magnitude", 1.0))
         # normed heads and values of another size: the per-head cache writer; a cap or slopes: no mma.sync kernel knows them
         self.plain_projection = (self.v_head_dim != head_dim or self.qk_norm_eps is not None or self.gate is not None
-                                 or self.shares_kv)
+                                 or self.shares_kv or self.magnitude != 1.0)
         self.shaped_scores = self.softcap is not None or self.distance_slopes is not None
         self.plain_only = self.plain_projection or self.shaped_scores
         if self.plain_only and (qkv_bias or o_bias):
@@ -102,7 +113,7 @@ class GQAAttention(Mixer):
             s[n["k"]] = ParamSpec((self.kv_size, self.hidden))
             s[n["v"]] = ParamSpec((self.v_size, self.hidden))
         if self.gate is not None:
-            s[n["g"]] = ParamSpec((self.o_in, self.hidden))
+            s[n["g"]] = ParamSpec((self.gate_rows, self.hidden))
         if self.qk_norm_weight:
             s[n["q_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="ones")
             if not self.shares_kv:
@@ -118,9 +129,18 @@ class GQAAttention(Mixer):
     def bind(self, params, compute_dtype):
         n = self.names
         # one product for everything that reads the mixer's input: q | k | v | gate (k, v absent with a borrowed cache)
-        w = torch.cat([params[n["q"]]] + ([] if self.shares_kv else [params[n["k"]], params[n["v"]]])
-                      + ([params[n["g"]]] if self.gate is not None else []), dim=0)
+        blocks = [params[n["q"]]] + ([] if self.shares_kv else [params[n["k"]], params[n["v"]]])
         self.gate_col = self.q_size + (0 if self.shares_kv else self.kv_size + self.v_size)
+        if self.gate is not None:
+            g = params[n["g"]]
+            pad = (-self.gate_col) % 8                    # the gate's columns start on a 16-byte boundary
+            if pad:
+                blocks.append(g.new_zeros((pad, self.hidden)))
+                self.gate_col += pad
+            blocks.append(g)
+            if (self.gate_col + self.gate_rows) % 8:      # and the rows of the product stay 16-byte aligned
+                blocks.append(g.new_zeros(((-(self.gate_col + self.gate_rows)) % 8, self.hidden)))
+        w = torch.cat(blocks, dim=0)
         if self.qk_norm_weight:
             self.q_norm_w = params[n["q_norm"]]
             self.k_norm_w = None if self.shares_kv else params[n["k_norm"]].to(self.q_norm_w.dtype)
@@ -138,7 +158,7 @@ class GQAAttention(Mixer):
 
     def cuda_modules(self, compute_dtype):
         mods = ["elementwise", "attention_generic"]
-        if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim:
+        if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim and not self.keep_first:
             mods += ["attention_decode", "attention_prefill_tc"]
             if not self.shaped_scores:
                 mods.append("attention_prefill")         # the mma.sync prompt kernel knows no cap and no slopes
@@ -150,13 +170,13 @@ class GQAAttention(Mixer):
         keeps_all = self.cache_keeps == "all"
         return KVRequest(self.n_kv_heads, self.head_dim, None if keeps_all else self.window,
                          None if self.v_head_dim == self.head_dim else self.v_head_dim,
-                         None if keeps_all else self.chunk)
+                         None if keeps_all else self.chunk, 0 if keeps_all else self.keep_first)
 
     # rows of the query tiles of the two tiled prefill kernels (csrc/attention_prefill.cu, attention_prefill_tc.cu)
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        return () if self.v_head_dim != self.head_dim else tuple(self.TILE_ROWS)
+        return () if self.v_head_dim != self.head_dim or self.keep_first else tuple(self.TILE_ROWS)
 
     def step_table(self, name, batch):
         """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
@@ -182,7 +202,7 @@ class GQAAttention(Mixer):
         q = self.project_into_cache(ctx, y, cache_view)                     # rotated q; k, v are in the cache
         o = self.attend(ctx, q, cache_view)
         if self.gate is not None:
-            o = kernels.sigmoid_gate(o, self._gate_cols)
+            o = kernels.sigmoid_gate(o, self._gate_cols, group=self.o_in // self.gate_rows)
         return o
 
     def _project_plain(self, ctx, y, view, rot, inv_freq):
@@ -193,7 +213,8 @@ class GQAAttention(Mixer):
         if isinstance(y, ScaledRows):
             y = y.materialize()
         common = dict(compute_dtype=ctx.compute_dtype, rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False),
-                      unit_norm_eps=self.qk_norm_eps, q_norm_weight=self.q_norm_w, k_norm_weight=self.k_norm_w)
+                      unit_norm_eps=self.qk_norm_eps, q_norm_weight=self.q_norm_w, k_norm_weight=self.k_norm_w,
+                      magnitude=self.magnitude)
         writes = view.writes and not self.shares_kv
         args = (self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim, inv_freq, ctx.tok_seq, ctx.tok_pos,
                 ctx.seq_slot, view.block_table, view.k_pages, view.v_pages, writes)
@@ -208,7 +229,7 @@ class GQAAttention(Mixer):
                     return kernels.head_norm_kv_write(kernels.gemm_simt(y, w, splits=splits), *args, **common)
         p = ctx.matmul(y, w)
         if self.gate is not None:
-            self._gate_cols = p[:, self.gate_col:self.gate_col + self.o_in]
+            self._gate_cols = p[:, self.gate_col:self.gate_col + self.gate_rows]
         return kernels.head_norm_kv_write(p, *args, **common)
 
     def project_into_cache(self, ctx, y, view):
@@ -223,6 +244,7 @@ class GQAAttention(Mixer):
         y, row_ss = ctx.unpack_rows(y, w, tc.PARTIAL)
         rot = dict((self.position.rotation() if self.position is not None else None) or dict(inv_freq=None, rot_dim=0))
         inv_freq = rot.pop("inv_freq")
+        rot.pop("magnitude", None)
         if self.plain_projection:
             return self._project_plain(ctx, y, view, rot, inv_freq)
         rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot,
@@ -254,6 +276,11 @@ class GQAAttention(Mixer):
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
         shaped = dict(softcap=self.softcap, slopes=self.slopes_dev, chunk=self.chunk)
         span = self.window or self.chunk                  # the most keys a query sees
+        if self.keep_first:
+            # kept first positions: the generic kernel walks them as a second stretch of keys before the window's
+            return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
+                                             ctx.seq_slot, view.block_table, self.scale, self.window,
+                                             v_head_dim=self.v_head_dim, keep_first=self.keep_first, **shaped)
         if self.v_head_dim != hd or (self.shaped_scores and ctx.compute_dtype != torch.bfloat16):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, self.window,

@@ -112,6 +112,14 @@ class NormedMean:
         self.branches, self.eps = list(branches), float(eps)
 
 
+class SumOf:
+    """A sub-layer's result that is still to be formed: the plain sum of ``addends`` (each float32 [T, H] or a stack
+    [S, T, H] of partial sums).  Whoever adds it to the stream forms it in the same pass."""
+
+    def __init__(self, addends):
+        self.addends = list(addends)
+
+
 class FeedForward(Part):
     """Position-wise transformation (dense here; routed experts would live behind the same face)."""
 

@@ -154,3 +154,82 @@ class SandwichBlock(Block):
         self._add(ctx, stream, r, self.post1, self.norm2, None)
         y = self.norm2.forward(ctx, stream)
         self._add(ctx, stream, self.ffn.output(ctx, y), self.post2, after, extra)
+
+
+def _leaves(prefix: str, part) -> Dict[str, Part]:
+    """{prefix: part}, or for a part made of parts (``leaf_parts``) its leaves under the joined prefixes."""
+    if hasattr(part, "leaf_parts"):
+        out: Dict[str, Part] = {}
+        for sub, leaf in part.leaf_parts().items():
+            out.update(_leaves(prefix + sub, leaf))
+        return out
+    return {prefix: part}
+
+
+@BLOCKS.register("scaled_prenorm")
+class ScaledPreNormBlock(Block):
+    """x += mult * mixer(norm1(x)); x += mult * ffn(norm2(x)), with one number ``mult`` for all sub-layers.  ``ffn`` (with
+    ``norm2``) may be None.
+
+    The sub-layers hand out their results in 32-bit (``output``: a tensor, a stack of partial sums, a ``NormedMean`` of
+    two mixers side by side, a ``SumOf``), and one kernel per sub-layer (``kernels.scaled_add``) forms the merge or the
+    sum, scales, adds into the 32-bit stream and, where the norm that reads the stream next is a Dynamic Tanh, computes
+    it in the same pass, so that norm never launches on its own (the first layer's and the final one apart).
+    """
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm = None, ffn: FeedForward = None, *, mult: float = 1.0,
+                 names: Dict[str, str] = None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("scaled_prenorm block: ffn and norm2 come together or not at all")
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.mult = float(mult)
+        self.names = dict(names)
+
+    def sub_parts(self) -> Dict[str, Part]:
+        out = {self.names["norm1"]: self.norm1}
+        out.update(_leaves(self.names["mixer"], self.mixer))
+        if self.ffn is not None:
+            out[self.names["norm2"]] = self.norm2
+            out.update(_leaves(self.names["ffn"], self.ffn))
+        elif self.names.get("norm2") is not None:
+            # a layer without feed-forward: a folder that stores the second norm all the same is not at fault
+            from ..weights.spec import ParamSpec
+            import dataclasses
+            out[""] = UnusedTensors({self.names["norm2"] + local: dataclasses.replace(spec, optional=True)
+                                     for local, spec in self.norm1.param_specs().items()})
+        return out
+
+    def entry_norm(self):
+        return self.norm1
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
+    def _add(self, ctx, stream, result, next_norm):
+        from .. import kernels
+        from .base import NormedMean, SumOf
+        eps = 0.0
+        if isinstance(result, NormedMean):
+            addends, eps = result.branches, result.eps
+        elif isinstance(result, SumOf):
+            addends = [(a, None) for a in result.addends]
+        else:
+            addends = [(result, None)]
+        nxt = next_norm.dyt_params() if next_norm is not None and hasattr(next_norm, "dyt_params") else None
+        stream.flush()
+        stream.prepared = None
+        y = kernels.scaled_add(stream.h, addends, self.mult, ctx.compute_dtype, eps=eps, next_dyt=nxt)
+        if y is not None:
+            stream.prepared = (next_norm, y)
+
+    def forward(self, ctx, stream, cache_view):
+        after = stream.after_block
+        stream.next_norm = None
+        y = self.norm1.forward(ctx, stream)
+        r = self.mixer.output(ctx, y, cache_view)
+        if self.ffn is None:
+            self._add(ctx, stream, r, after)
+            return
+        self._add(ctx, stream, r, self.norm2)
+        y = self.norm2.forward(ctx, stream)
+        self._add(ctx, stream, self.ffn.output(ctx, y), after)

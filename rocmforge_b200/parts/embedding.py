@@ -60,8 +60,11 @@ class OutputHead(Part):
     """logits = W y in float32; with tied embeddings W is the embedding matrix itself
     (maeddesg/ROCmForge src/gpu/forward.rs:1313-1338; tie: src/gpu/weights.rs:868-886)."""
 
-    def __init__(self, vocab: int, hidden: int, tied_to: Optional[str] = None, param_name: str = "weight"):
+    def __init__(self, vocab: int, hidden: int, tied_to: Optional[str] = None, param_name: str = "weight",
+                 softcap: Optional[float] = None):
+        """``softcap``: logits <- softcap * tanh(logits / softcap), in 32-bit."""
         self.vocab, self.hidden, self.tied_to, self.param_name = vocab, hidden, tied_to, param_name
+        self.softcap = float(softcap) if softcap else None
         self.linear: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -70,5 +73,9 @@ class OutputHead(Part):
     def bind(self, params, compute_dtype):
         self.linear = Linear(params[self.param_name])
 
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"] if self.softcap is not None else []
+
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
-        return self.linear(ctx, y, out_f32=True)
+        logits = self.linear(ctx, y, out_f32=True)
+        return kernels.softcap_(logits, self.softcap) if self.softcap is not None else logits

@@ -24,25 +24,28 @@ class GatedMLP(FeedForward):
 
     accepts_scaled_rows = True
 
-    def __init__(self, hidden: int, intermediate: int, activation: str = "silu"):
+    def __init__(self, hidden: int, intermediate: int, activation: str = "silu", names: Optional[Dict[str, str]] = None):
+        """``names``: the tensors' names below the part's prefix (keys gate, up, down)."""
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} has no kernel")
         self.hidden, self.intermediate = hidden, intermediate
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {
-            "gate_proj.weight": ParamSpec((self.intermediate, self.hidden)),
-            "up_proj.weight": ParamSpec((self.intermediate, self.hidden)),
-            "down_proj.weight": ParamSpec((self.hidden, self.intermediate)),
+            self.names["gate"]: ParamSpec((self.intermediate, self.hidden)),
+            self.names["up"]: ParamSpec((self.intermediate, self.hidden)),
+            self.names["down"]: ParamSpec((self.hidden, self.intermediate)),
         }
 
     def bind(self, params, compute_dtype):
-        g, u = params["gate_proj.weight"], params["up_proj.weight"]
+        g, u = params[self.names["gate"]], params[self.names["up"]]
         gu = torch.stack([g, u], dim=1).reshape(2 * self.intermediate, self.hidden).contiguous()
         self.gate_up = Linear(gu)
-        self.down = Linear(params["down_proj.weight"])
+        self.down = Linear(params[self.names["down"]])
 
     def cuda_modules(self, compute_dtype):
         return ["elementwise"]
@@ -88,3 +91,31 @@ class SquaredReluMLP(FeedForward):
 
     def output(self, ctx, y):
         return self.down.f32_parts(ctx, self.activated(ctx, y))
+
+
+@FEED_FORWARDS.register("sum")
+class SummedFeedForward(FeedForward):
+    """Feed-forwards side by side on the same input whose results are added (routed experts and an expert that every token
+    uses, say).  ``branches``: {prefix below this part's: feed-forward}; at most two.  The sum is formed by whoever adds
+    the result to the stream (the part hands out a ``SumOf``)."""
+
+    def __init__(self, branches: Dict[str, FeedForward]):
+        if not 1 <= len(branches) <= 2:
+            raise ValueError("summed feed-forward: one or two branches")
+        self.branches = dict(branches)
+
+    def leaf_parts(self):
+        return dict(self.branches)
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
+    def output(self, ctx, y):
+        from ..engine.stream import ScaledRows
+        from .base import SumOf
+        if isinstance(y, ScaledRows):
+            y = y.materialize()
+        return SumOf([f.output(ctx, y) for f in self.branches.values()])
+
+    def forward(self, ctx, y, stream):
+        raise NotImplementedError("summed feed-forward: its result is added by the block that holds it (output)")

@@ -49,3 +49,43 @@ class RMSNorm(Norm):
         if rows is None:
             stream.pending = None           # the kernel added it into h
         return y
+
+
+@NORMS.register("dyt")
+class DynamicTanh(Norm):
+    """y_i = tanh(alpha x_i) * w_i + b_i with one learned number alpha: a norm that computes no statistics of its row,
+    evaluated in 32-bit.  Tensors: the weight ``param_name``, and ``<param_name>.alpha`` (no dimensions) and
+    ``<param_name>.b`` beside it.  Whoever updates the stream last may run it in the same pass (``dyt_params``) and leave
+    the result in ``stream.prepared``."""
+
+    def __init__(self, size: int, param_name: str = "weight"):
+        self.size, self.param_name = size, param_name
+        self.weight = self.bias = self.alpha = None
+        self.compute_dtype = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n = self.param_name
+        return {n: ParamSpec((self.size,), kind="vector", init="ones"),
+                n + ".alpha": ParamSpec((), kind="vector", init="ones"),
+                n + ".b": ParamSpec((self.size,), kind="vector", init="zeros")}
+
+    def bind(self, params, compute_dtype):
+        n = self.param_name
+        # the kernels take these three in 32-bit (from bfloat16 the conversion is exact)
+        self.weight = params[n].to(torch.float32).contiguous()
+        self.bias = params[n + ".b"].to(torch.float32).contiguous()
+        self.alpha = params[n + ".alpha"].to(torch.float32).reshape(1).contiguous()
+        self.compute_dtype = compute_dtype
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
+    def dyt_params(self):
+        return (self.alpha, self.weight, self.bias)
+
+    def forward(self, ctx, stream, rows=None, deferred_ok=False):
+        prepared, stream.prepared = stream.prepared, None
+        if prepared is not None and prepared[0] is self and rows is None and stream.pending is None:
+            return prepared[1]
+        stream.flush()
+        return kernels.dyt_rows(stream.h, self.alpha, self.weight, self.bias, self.compute_dtype, rows=rows)

@@ -55,3 +55,42 @@ class NeoxRope(PositionEncoding):
 
     def rotation(self):
         return dict(inv_freq=self.inv_freq, rot_dim=self.rotary_dim, interleaved=self.interleaved)
+
+
+@POSITIONS.register("rope_yarn")
+class YarnRope(NeoxRope):
+    """The same rotation with frequencies stretched over a ramp of pair indices and with longer pairs (YaRN).
+
+    With f_i = theta^(-2i/d), d the rotary size, and index(t) = d ln(original / (2 pi t)) / (2 ln theta), the pair index
+    at which a pair makes t turns over ``original`` positions:
+
+        lo = max(floor(index(fast)), 0),  hi = min(ceil(index(slow)), d - 1)
+        ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+        frequency_i = (f_i / factor) ramp_i + f_i (1 - ramp_i)
+
+    so pairs that turn more than ``fast`` times keep their frequency and pairs that turn less than ``slow`` times turn
+    ``factor`` times slower.  Sine and cosine are multiplied by ``magnitude`` = 0.1 ln(factor) + 1, which the rotation
+    kernel receives beside the frequencies (a pair grows by that factor: it is no pure rotation).
+    """
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False, *, factor: float,
+                 original: float, fast: float, slow: float):
+        super().__init__(head_dim, theta, rotary_dim, interleaved)
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and theta > 1):
+            raise ValueError(f"rope_yarn needs positive factor, original, fast and slow and theta > 1; got {factor}, "
+                             f"{original}, {fast}, {slow}, {theta}")
+        d = self.rotary_dim
+        self.yarn = dict(factor=float(factor), original=float(original), fast=float(fast), slow=float(slow))
+
+        def index_of(turns: float) -> float:
+            return d * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+        lo = max(math.floor(index_of(fast)), 0)
+        hi = min(math.ceil(index_of(slow)), d - 1)
+        i = torch.arange(d // 2, dtype=torch.float64)
+        f = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / d)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        self.inv_freq_host = (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32)
+        self.magnitude = 0.1 * math.log(factor) + 1.0
+
+    def rotation(self):
+        return dict(super().rotation(), magnitude=self.magnitude)

@@ -104,6 +104,9 @@ def fill_normal_device(n: int, key: int, std: float, dtype: torch.dtype, device)
 
 
 def random_tensor(name: str, spec: ParamSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    if spec.init == "normal" and spec.mean != 0.0 and spec.kind != "int_table":
+        centred = random_tensor(name, ParamSpec(spec.shape, spec.kind, "normal", spec.std), seed, dtype, device)
+        return (centred.to(torch.float32) + spec.mean).to(dtype)
     if spec.init == "ones":
         return torch.ones(spec.shape, dtype=dtype, device=device)
     if spec.init == "zeros":

@@ -13,7 +13,7 @@ class ParamSpec:
              "vector": norm weight or bias; a vector stored in 32-bit stays 32-bit,
              one stored in bfloat16 stays bfloat16 (all 32-bit on the float32 path).
              "int_table": integer table, kept as int32.
-    init     how the random-weights mode fills it: "normal" (mean 0, ``std``), "ones", "zeros".
+    init     how the random-weights mode fills it: "normal" (``mean``, ``std``), "ones", "zeros".
     tied_to  full name of another tensor that stands in when this one is absent.
     optional a tensor that a folder may hold or not (one that the model does not use: a file that has it is not at
              fault, and the random-weights mode does not make it).
@@ -22,5 +22,6 @@ class ParamSpec:
     kind: str = "matrix"
     init: str = "normal"
     std: float = 0.02
+    mean: float = 0.0
     tied_to: Optional[str] = None
     optional: bool = False
