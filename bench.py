@@ -451,6 +451,27 @@ def vilulorn_shape(width, layers=4):
     return vil, rifizen_shape(width, layers)[0]
 
 
+def figalix_shape(width, layers=4):
+    """A Figalix configuration with layers of the size a real model has: attention over a window of 1,024 that keeps a
+    sequence's first 4 positions (128-element heads, half of each rotated with stretched frequencies, a quarter as many kv
+    heads, a gate per head) beside a matrix memory of 128 x 128 per head, alternating with Mamba-2 layers (inner = 2 x
+    width in heads of 64, a state of 128 x 64 per head, one group, 4 taps); a dense feed-forward of 4 x width alternating
+    with 16 experts of width each (2 per token) plus a shared one.  And the Rifizen configuration of equal width, heads
+    and depth (its closest relative here: attention over a window beside a matrix state per head, dense and routed
+    feed-forwards in turn)."""
+    heads = width // 128
+    left = dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, mask={"size": 1024, "keep_first": 4},
+                scale=128 ** -0.5, rot=dict(dims=64, base=1e6, scaling=dict(factor=8.0, original=8192, fast=32.0, slow=1.0)))
+    right = dict(heads=heads, dim=128, vdim=128, gate_cap=15.0)
+    ssm = dict(heads=2 * width // 64, vdim=64, state=128, groups=1, conv=4, norm_groups=1)
+    dense = dict(kind="dense", ff=4 * width)
+    moe = dict(kind="moe", expert=dict(ff=width), router=dict(experts=16, top=2), shared=dict(ff=width))
+    fig = dict(architecture="Figalix", vocab=32000, width=width, norm=dict(eps=1e-6), residual_mult=0.5, logit_softcap=30.0,
+               layers=[dict(type="parallel", mixer=dict(left=left, right=right), mlp=dense if i % 4 == 0 else moe) if i % 2 == 0
+                       else dict(type="mamba2", mixer=ssm, mlp=moe if i % 4 == 1 else dense) for i in range(layers)])
+    return fig, rifizen_shape(width, layers)[0]
+
+
 def rifizen_points(pk, seed, widths=(1024, 2048), tokens=PREFILL_TOKENS, batches=(8, 64), steps=64, warmup=8,
                    names=("rifizen", "dense"), archs=("Rifizen", "Qwen2ForCausalLM"), shapes=None):
     """Prefill and decode of one design at layer sizes of a real model, beside another at equal size (by default Rifizen
@@ -564,7 +585,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen", "vilulorn"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen", "vilulorn", "figalix"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
                     help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
@@ -598,6 +619,12 @@ def main():
                           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
                           **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup, names=("vilulorn", "rifizen"),
                                            archs=("Vilulorn", "Rifizen"), shapes=vilulorn_shape)}))
+        return 0
+    if args.only == "figalix":
+        print(json.dumps({"only": "figalix", "tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
+                          "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
+                          **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup, names=("figalix", "rifizen"),
+                                           archs=("Figalix", "Rifizen"), shapes=figalix_shape)}))
         return 0
     if args.only in ("0.5b", "14b"):
         print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))

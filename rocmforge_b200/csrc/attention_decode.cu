@@ -333,7 +333,7 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
                               int out_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                               const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
                               int nh, int nkv, float scale, int window, int splits, int* __restrict__ status,
-                              float softcap, const float* __restrict__ slopes) {
+                              float softcap, const float* __restrict__ slopes, int keep_first) {
     constexpr int HD = EPL * 32;
     constexpr int NT = WARPS * 32;
     constexpr int HALVES = HD / 64;                             // 128-byte column blocks of a row
@@ -368,7 +368,13 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         for (int h = 0; h < 2; ++h)
             if (tig * 2 + h < G) slope2[h] = slopes[kvh * G + tig * 2 + h];
     const int p_lo = lo / RF_PAGE, p_hi = pos / RF_PAGE;
-    const int n_my = (p_hi - p_lo - rank) >= 0 ? (p_hi - p_lo - rank) / splits + 1 : 0;     // pages of this CTA
+    // with a window the sequence's first keep_first positions stay visible: the pages below the window's first that hold
+    // some of them come first in the list of pages that the cluster's CTAs deal out among themselves (kept positions in
+    // the window's own pages are a matter of the mask)
+    int n_kept = keep_first > 0 ? (keep_first + RF_PAGE - 1) / RF_PAGE : 0;
+    if (n_kept > p_lo) n_kept = p_lo;
+    const int n_listed = n_kept + p_hi - p_lo + 1;
+    const int n_my = (n_listed - 1 - rank) >= 0 ? (n_listed - 1 - rank) / splits + 1 : 0;   // pages of this CTA
     const int n_units = n_my * UPP;
     const int* bt = block_table + (size_t)seq_slot[tok_seq[b]] * max_pages;
     uint8_t* my_k = ring + (size_t)warp * 2 * TILE;
@@ -388,17 +394,18 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
     // push (every CTA has long arrived by then, so the wait costs nothing)
     if (splits > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
-    // tile u of this CTA: page p_lo + rank + (u / UPP) * splits, rows (u % UPP) * ROWS ... of it
-    auto first_key = [&](int u) { return (p_lo + rank + (u / UPP) * splits) * RF_PAGE + (u % UPP) * ROWS; };
-    auto next_tile = [&](int u) {                     // the next of this warp's tiles that holds a key in [lo, pos]
+    // tile u of this CTA: entry rank + (u / UPP) * splits of the list of pages, rows (u % UPP) * ROWS ... of it
+    auto page_of = [&](int u) { const int e = rank + (u / UPP) * splits; return e < n_kept ? e : p_lo + e - n_kept; };
+    auto first_key = [&](int u) { return page_of(u) * RF_PAGE + (u % UPP) * ROWS; };
+    auto next_tile = [&](int u) {                     // the next of this warp's tiles that holds a visible key
         for (u += WARPS; u < n_units; u += WARPS) {
             const int k0 = first_key(u);
-            if (k0 <= pos && k0 + ROWS - 1 >= lo) break;
+            if (k0 <= pos && (k0 + ROWS - 1 >= lo || k0 < keep_first)) break;
         }
         return u;
     };
     auto issue = [&](int u, bool keys) {              // lane 0: the keys or the values of tile u into this warp's buffer
-        const int page = bt[p_lo + rank + (u / UPP) * splits];
+        const int page = bt[page_of(u)];
         const int row = (page * nkv + kvh) * RF_PAGE + (u % UPP) * ROWS;
         const uint32_t bar = keys ? bar_k : bar_v, dst = keys ? k_t : v_t;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(TILE) : "memory");
@@ -455,6 +462,8 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         const int key0 = first_key(u);
         int k_begin = lo - key0; if (k_begin < 0) k_begin = 0;                    // valid rows of this tile
         int k_last = pos - key0; if (k_last > ROWS - 1) k_last = ROWS - 1;
+        int k_kept = keep_first - key0; if (k_kept > k_last + 1) k_kept = k_last + 1;  // rows below it are kept first positions
+        if (k_kept < 0) k_kept = 0;
         if (!wait(bar_k, it & 1)) { failed = true; break; }
         // ---- scores, transposed: [0] (key gid, head tig*2), [1] (key gid, head tig*2+1), [2], [3] the same for key gid + 8
         float sc[NB][4];
@@ -489,7 +498,7 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
                     if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
                     v -= slope2[e & 1] * (float)(pos - (key0 + kk));
                 }
-                sc[kb][e] = (kk >= k_begin && kk <= k_last) ? v : -INFINITY;
+                sc[kb][e] = ((kk >= k_begin && kk <= k_last) || kk < k_kept) ? v : -INFINITY;
                 mx[e & 1] = fmaxf(mx[e & 1], sc[kb][e]);
             }
         float corr[2], psum[2] = {0.f, 0.f};
@@ -528,12 +537,12 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
             oc[mt][0] *= corr[0]; oc[mt][1] *= corr[1]; oc[mt][2] *= corr[0]; oc[mt][3] *= corr[1];
         }
         if (!wait(bar_v, it & 1)) { failed = true; break; }
-        if (k_begin > 0 || k_last < ROWS - 1) {
+        if ((k_begin > 0 && k_kept < ROWS) || k_last < ROWS - 1) {
             // rows outside the sequence get weight zero, but 0 * (whatever bits lie there) must be 0
             // (the swizzle permutes 16-byte pieces inside a row: clearing whole rows needs no address math)
             for (int i = lane; i < ROWS * HALVES * 8; i += 32) {
                 const int row = (i >> 3) % ROWS, h = i / (ROWS * 8);
-                if (row < k_begin || row > k_last)
+                if ((row < k_begin || row > k_last) && row >= k_kept)
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_t + h * HALF_BYTES + row * 128 + (i & 7) * 16),
                                  "r"(0u) : "memory");
             }
@@ -542,7 +551,7 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         }
 #pragma unroll
         for (int kb = 0; kb < NB; ++kb) {
-            if (kb * 16 > k_last || kb * 16 + 15 < k_begin) continue;             // a block without a key of the sequence
+            if ((kb * 16 > k_last || kb * 16 + 15 < k_begin) && kb * 16 >= k_kept) continue;   // a block without a visible key
 #pragma unroll
             for (int mt = 0; mt < HD / 16; ++mt) {
                 // V^T: matrices (keys + 0..7, dims mt*16 + 0..7), (same keys, dims + 8), (keys + 8.., dims), (keys + 8.., dims + 8)
@@ -683,7 +692,8 @@ template <int EPL, int ROWS, int WARPS>
 static int launch_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
                         const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, float scale,
-                        int window, int B, int splits, int* status, float softcap, const float* slopes, cudaStream_t st) {
+                        int window, int B, int splits, int* status, float softcap, const float* slopes, int keep_first,
+                        cudaStream_t st) {
     constexpr int HD = EPL * 32;
     const size_t smem = (size_t)WARPS * 2 * ROWS * HD * 2 +
                         (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 16 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
@@ -724,7 +734,7 @@ static int launch_warps(const void* q, int q_stride, void* out, int out_stride, 
         return me;
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_warps_kernel<EPL, ROWS, WARPS>, mk, mv,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride, tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status, softcap, slopes);
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status, softcap, slopes, keep_first);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -774,20 +784,22 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
 
 // A warp per tile of keys, `warps` (4 or 8) warps per CTA.
 // softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
-// lowered by slopes[head] * (query position - key position).
+// lowered by slopes[head] * (query position - key position).  keep_first: with a window (window > 0), the first keep_first
+// positions of a sequence stay visible as well.
 int rf_attention_decode_warps_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                   const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
                                   const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
                                   float scale, int window, int B, int splits, int warps, float softcap, const float* slopes,
-                                  int* status, cudaStream_t st) {
+                                  int keep_first, int* status, cudaStream_t st) {
     if (B <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (!rf_attention_decode_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
     if (nkv > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return RF_ERR_BAD_ARG;
     if (warps != 4 && warps != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
 #define GOW(EPL, ROWS, WARPS) return launch_warps<EPL, ROWS, WARPS>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, \
-                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, softcap, slopes, st)
+                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, softcap, slopes, keep_first, st)
     if (hd == 64) { if (warps == 8) GOW(2, 32, 8); GOW(2, 32, 4); }
     if (hd == 128) { if (warps == 8) GOW(4, 32, 8); GOW(4, 32, 4); }
     if (warps == 8) GOW(8, 16, 8);
@@ -801,7 +813,7 @@ int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_st
                               float scale, int window, int B, int splits, int warps, int* status, cudaStream_t st) {
     return rf_attention_decode_warps_ext(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, tok_pos, seq_slot,
                                          block_table, max_pages, nh, nkv, hd, scale, window, B, splits, warps, 0.f, nullptr,
-                                         status, st);
+                                         0, status, st);
 }
 
 int rf_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -87,7 +87,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_start, const int* __restrict__ seq_nnew,
                             const int* __restrict__ cu_q, const int* __restrict__ block_table, int max_pages,
                             int nh, int nkv, float scale, int window, int* __restrict__ status, float softcap,
-                            const float* __restrict__ slopes) {
+                            const float* __restrict__ slopes, int keep_first) {
     constexpr int HALVES = HD / 64;                     // 128-byte column blocks of a head
     constexpr uint32_t QH_BYTES = AT_BM * 128;          // one column block of the Q tile (also the P tile)
     constexpr uint32_t Q_BYTES = HALVES * QH_BYTES;
@@ -130,7 +130,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int pos_first = start + q0, pos_last = pos_first + rows_here - 1, seq_last = start + n_new - 1;
     const int lo_first = rf_first_key(pos_first, window);
     const int kt_lo = lo_first / AT_BN, kt_hi = pos_last / AT_BN;      // AT_BN == RF_PAGE: a tile is a page
-    const int n_kt = kt_hi - kt_lo + 1;
+    // with a window the sequence's first keep_first positions stay visible: the pages below the window's first that hold
+    // some of them are walked before the window's (kept positions in the window's own pages are a matter of the mask)
+    int n_kept = keep_first > 0 ? (keep_first + AT_BN - 1) / AT_BN : 0;
+    if (n_kept > kt_lo) n_kept = kt_lo;
+    const int n_kt = n_kept + kt_hi - kt_lo + 1;
+    auto page_of = [&](int t) { return t < n_kept ? t : kt_lo + t - n_kept; };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -168,7 +173,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int t = 0; t < n_kt; ++t) {
                 const int st = t & 1;
                 uint8_t* kd = kv_s + (size_t)st * 2 * KV_BYTES;
-                const int row = (bt[kt_lo + t] * nkv + kvh) * RF_PAGE;
+                const int row = (bt[page_of(t)] * nkv + kvh) * RF_PAGE;
                 if (!mbar_wait(b_kfree + 8 * st, ((t >> 1) & 1) ^ 1, &abort_flag)) break;
                 mbar_expect_tx(b_kfull + 8 * st, KV_BYTES);
                 for (int h = 0; h < HALVES; ++h)
@@ -235,7 +240,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool ok = true;
         for (int t = 0; t < n_kt; ++t) {
             const int st = t & 1;
-            const int key0 = (kt_lo + t) * AT_BN;
+            const int key0 = page_of(t) * AT_BN;
             ok = mbar_wait(b_sfull + 8 * st, (t >> 1) & 1, &abort_flag);
             if (!ok) break;
             tcgen05_fence_after();
@@ -254,7 +259,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             const bool no_mask = key0 + AT_BN - 1 <= pos_first && rows_here == AT_BM &&
-                                 key0 >= rf_first_key(pos_last, window);
+                                 (key0 >= rf_first_key(pos_last, window) || key0 + AT_BN <= keep_first);
             // the row of S, once, into registers (raw products; masked ones -inf).  Maximum and sum are kept
             // in four independent partial results each: one warp per scheduler cannot hide a chain of 64
             // dependent operations
@@ -286,7 +291,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int j = 0; j < AT_BN; ++j) {
                     const int key = key0 + j;
-                    if (!(row_ok && key <= pos_i && key >= lo_i)) sc[j] = -INFINITY;
+                    if (!(row_ok && key <= pos_i && (key >= lo_i || key < keep_first))) sc[j] = -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -386,7 +391,7 @@ template <int HD>
 static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
-                     int* status, float softcap, const float* slopes, cudaStream_t st) {
+                     int* status, float softcap, const float* slopes, int keep_first, cudaStream_t st) {
     constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 15 * 8 + 16;
     static bool configured = false;
     if (!configured) {
@@ -397,7 +402,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     }
     cudaError_t e = rf_launch(attention_prefill_tc_kernel<HD>, dim3(nh, n_tiles), dim3(AT_THREADS), smem, st, mq, mk, mv,
                               reinterpret_cast<__nv_bfloat16*>(out), out_stride, tiles, seq_slot, seq_start, seq_nnew, cu_q,
-                              block_table, max_pages, nh, nkv, scale, window, status, softcap, slopes);
+                              block_table, max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -413,13 +418,15 @@ int rf_attention_prefill_tc_supported(int nh, int nkv, int hd) {
 // tiles: n_tiles pairs (sequence index, first new-token row of the tile within the sequence), 128 rows a tile.
 // q: [T, q_stride] with the heads' columns first; T is needed for the map's extent.
 // softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
-// lowered by slopes[head] * (query position - key position).
+// lowered by slopes[head] * (query position - key position).  keep_first: with a window (window > 0), the first keep_first
+// positions of a sequence stay visible to every later query as well.
 int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
                                 const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
                                 int max_pages, int nh, int nkv, int hd, float scale, int window, float softcap,
-                                const float* slopes, int* status, cudaStream_t st) {
+                                const float* slopes, int keep_first, int* status, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (n_tiles > 65535) return RF_ERR_UNSUPPORTED;      // tiles are the grid's y dimension (8 million prompt tokens)
     if (!rf_attention_prefill_tc_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (out_stride % 8)) return RF_ERR_BAD_ARG;
@@ -431,9 +438,9 @@ int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, i
         return e;
     if (hd == 64)
         return at_launch<64>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                             max_pages, nh, nkv, scale, window, status, softcap, slopes, st);
+                             max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, st);
     return at_launch<128>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                          max_pages, nh, nkv, scale, window, status, softcap, slopes, st);
+                          max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, st);
 }
 
 int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
@@ -443,7 +450,7 @@ int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int o
                             cudaStream_t st) {
     return rf_attention_prefill_tc_ext(q, q_stride, T, out, out_stride, k_pages, v_pages, n_pages, tiles, n_tiles, seq_slot,
                                        seq_start, seq_nnew, cu_q, block_table, max_pages, nh, nkv, hd, scale, window, 0.f,
-                                       nullptr, status, st);
+                                       nullptr, 0, status, st);
 }
 
 }

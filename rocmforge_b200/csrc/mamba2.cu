@@ -37,6 +37,65 @@ conv_silu_kernel(const T* __restrict__ src, int row_stride, int col0, const floa
     }
 }
 
+// The same for rows whose channels come in whole groups of four (C, col0 and row_stride multiples of 4): a thread owns
+// four neighbouring channels with their TAPS x 4 weights in registers and walks CV_TOK tokens; the inputs are 8- or
+// 16-byte loads, the result one 16-byte store.  The sum of a channel runs over the taps in the same order as above.
+#define CV_TOK 4
+
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float* x) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* x) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xffff0000u);
+        x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xffff0000u);
+    }
+};
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(256)
+conv_silu_vec_kernel(const T* __restrict__ src, int row_stride, int col0, const float* __restrict__ state,
+                     const void* __restrict__ w, const void* __restrict__ bias, int w_is_f32, float* __restrict__ out,
+                     const int* __restrict__ tok_seq, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int C,
+                     int T_) {
+    pdl_trigger();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    const int t0 = blockIdx.x * CV_TOK;
+    if (c >= C) return;
+    float wt[TAPS][4], bs[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        bs[u] = load_vec(bias, w_is_f32, c + u);
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wt[j][u] = load_vec(w, w_is_f32, (c + u) * TAPS + j);
+    }
+    pdl_wait();
+    for (int t = t0; t < t0 + CV_TOK && t < T_; ++t) {
+        const int b = tok_seq[t];
+        const int r = t - cu_q[b];
+        const float* old = state + (size_t)seq_slot[b] * (TAPS - 1) * C;
+        float acc[4] = {bs[0], bs[1], bs[2], bs[3]};
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const int back = TAPS - 1 - j;
+            float x[4];
+            if (r - back >= 0) Vec4<T>::load(src + (size_t)(t - back) * row_stride + col0 + c, x);
+            else Vec4<float>::load(old + (size_t)(TAPS - 1 + r - back) * C + c, x);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = fmaf(wt[j][u], x[u], acc[u]);
+        }
+        float4 y;
+        y.x = acc[0] / (1.f + expf(-acc[0])); y.y = acc[1] / (1.f + expf(-acc[1]));
+        y.z = acc[2] / (1.f + expf(-acc[2])); y.w = acc[3] / (1.f + expf(-acc[3]));
+        *reinterpret_cast<float4*>(out + (size_t)t * C + c) = y;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_state_update_kernel(const T* __restrict__ src, int row_stride, int col0, float* __restrict__ state,
@@ -107,11 +166,22 @@ static int launch_conv(const void* src, int row_stride, int col0, float* state, 
                        cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (taps < 1 || taps > MB_MAX_TAPS || C <= 0) return RF_ERR_UNSUPPORTED;
+    const bool groups_of_four = C % 4 == 0 && col0 % 4 == 0 && row_stride % 4 == 0 && taps <= 4 &&
+                                (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0;
+    if (groups_of_four && T_ >= 64) {
+        const dim3 grid((T_ + CV_TOK - 1) / CV_TOK, (C / 4 + 255) / 256);
+#define CONV_VEC(TAPS) rf_launch(conv_silu_vec_kernel<T, TAPS>, grid, dim3(256), 0, st, reinterpret_cast<const T*>(src), row_stride, \
+                                 col0, (const float*)state, w, bias, w_is_f32, out, tok_seq, cu_q, seq_slot, C, T_)
+        if (taps == 1) CONV_VEC(1); else if (taps == 2) CONV_VEC(2); else if (taps == 3) CONV_VEC(3); else CONV_VEC(4);
+#undef CONV_VEC
+        RF_LAUNCH_CHECK();
+    } else {
     int by = T_ >= 296 ? 1 : (C + 255) / 256;
     if (by > 64) by = 64;
     rf_launch(conv_silu_kernel<T>, dim3(T_, by), dim3(256), 0, st, reinterpret_cast<const T*>(src), row_stride, col0,
               (const float*)state, w, bias, w_is_f32, out, tok_seq, cu_q, seq_slot, C, taps);
     RF_LAUNCH_CHECK();
+    }
     if (taps > 1) {
         int cy = (C + 255) / 256;
         if (cy > 64) cy = 64;

@@ -43,8 +43,8 @@ class GQAAttention(Mixer):
     their own positions; the cache keeps their pages) and ``gate`` "sigmoid_head" (one gate per head, W_g of ``heads``
     rows: head h's output is multiplied by sigmoid(W_g x)_h).  A position encoding whose rotation carries a ``magnitude``
     (sine and cosine times a factor) goes through the per-head writer as well.  Normed heads and values of another size go into the
-    cache through the per-head writer; a cap and slopes are known to the generic attention and to the tcgen05 prompt
-    attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
+    cache through the per-head writer; a cap, slopes and kept first positions are known to the generic attention and to the
+    tcgen05 prompt attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
     on the same kernels as one without them.
     """
 
@@ -158,9 +158,9 @@ class GQAAttention(Mixer):
 
     def cuda_modules(self, compute_dtype):
         mods = ["elementwise", "attention_generic"]
-        if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim and not self.keep_first:
+        if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim:
             mods += ["attention_decode", "attention_prefill_tc"]
-            if not self.shaped_scores:
+            if not self.shaped_scores and not self.keep_first:
                 mods.append("attention_prefill")         # the mma.sync prompt kernel knows no cap and no slopes
         return mods
 
@@ -176,7 +176,9 @@ class GQAAttention(Mixer):
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        return () if self.v_head_dim != self.head_dim or self.keep_first else tuple(self.TILE_ROWS)
+        if self.v_head_dim != self.head_dim:
+            return ()
+        return ("attention_tiles128",) if self.keep_first else tuple(self.TILE_ROWS)
 
     def step_table(self, name, batch):
         """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
@@ -276,15 +278,13 @@ class GQAAttention(Mixer):
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
         shaped = dict(softcap=self.softcap, slopes=self.slopes_dev, chunk=self.chunk)
         span = self.window or self.chunk                  # the most keys a query sees
-        if self.keep_first:
-            # kept first positions: the generic kernel walks them as a second stretch of keys before the window's
+        # kept first positions: the generic kernel, the tcgen05 prompt kernel and the clustered decode kernel walk the
+        # pages that hold them before the window's
+        kept = dict(keep_first=self.keep_first)
+        if self.v_head_dim != hd or ((self.shaped_scores or self.keep_first) and ctx.compute_dtype != torch.bfloat16):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, self.window,
-                                             v_head_dim=self.v_head_dim, keep_first=self.keep_first, **shaped)
-        if self.v_head_dim != hd or (self.shaped_scores and ctx.compute_dtype != torch.bfloat16):
-            return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
-                                             ctx.seq_slot, view.block_table, self.scale, self.window,
-                                             v_head_dim=self.v_head_dim, **shaped)
+                                             v_head_dim=self.v_head_dim, **shaped, **kept)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
             if ctx.options.clustered_decode:
@@ -293,8 +293,8 @@ class GQAAttention(Mixer):
                 return kernels.attention_decode_warps(
                     q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                     view.block_table, self.scale, self.window,
-                    splits=kernels.decode_splits(ctx.B, nkv, longest, span), **shaped)
-            if not self.shaped_scores and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
+                    splits=kernels.decode_splits(ctx.B, nkv, longest, span), **shaped, **kept)
+            if not self.shaped_scores and not self.keep_first and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
                 # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
                 max_chunks = 1
@@ -317,10 +317,10 @@ class GQAAttention(Mixer):
                 and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
             return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles128,
                                                 ctx.seq_slot, ctx.seq_start, ctx.seq_nnew, ctx.cu_q,
-                                                view.block_table, self.scale, self.window, **shaped)
-        if self.shaped_scores:
+                                                view.block_table, self.scale, self.window, **shaped, **kept)
+        if self.shaped_scores or self.keep_first:
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
-                                             ctx.seq_slot, view.block_table, self.scale, self.window, **shaped)
+                                             ctx.seq_slot, view.block_table, self.scale, self.window, **shaped, **kept)
         if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and tiles64 is not None and tiles64.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
                 and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):

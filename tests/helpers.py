@@ -256,3 +256,101 @@ def write_vilulorn(cfg: dict, folder: str, dtype: str = "float32") -> None:
     c, raw = vilulorn_config(cfg)
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     rf.write_model_folder(folder, raw, architecture_for("Vilulorn").build(c).param_specs(), cfg["seed"], dt)
+
+
+# --------------------------------------------------------------------------- Figalix
+
+def _kept_window(*, heads, kv_heads, dim, vdim, scale, window=None, keep_first=None, rot_dims=0, rot_base=None, scaling=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if window is not None or keep_first is not None:
+        m["mask"] = {}
+        if window is not None:
+            m["mask"]["size"] = window
+        if keep_first is not None:
+            m["mask"]["keep_first"] = keep_first
+    if rot_dims:
+        m["rot"] = {"dims": rot_dims, "base": rot_base}
+        if scaling is not None:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return m
+
+
+def _side_by_side(left, *, heads, dim, vdim, gate_cap, mlp):
+    right = {"heads": heads, "dim": dim, "vdim": vdim}
+    if gate_cap is not None:
+        right["gate_cap"] = gate_cap
+    return {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+
+
+def _ssd(*, heads, vdim, state, groups, conv, norm_groups, mlp):
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv,
+                                        "norm_groups": norm_groups}, "mlp": mlp}
+
+
+def _shares(ff, experts, top, shared=None):
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared is not None:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+# Sizes that differ from each other in every respect: which kind of layer comes first, values of another size than keys,
+# as many kv heads as heads and one for all, heads rotated wholly, partly (with and without stretched frequencies) and not
+# at all, windows of 1, below a page, above one and absent, first positions kept: none, fewer than the window, more than
+# the window, more than a page; a matrix memory of 256 x 8 and of 16 x 200, gates capped tightly, loosely and not at all;
+# state-space layers with one group, as many groups as heads and in between, one to seven taps, a norm in one part and in
+# several, states that are no multiple of eight; layers without feed-forward, dense ones, one expert a token and all of
+# them, with and without the shared expert; multipliers of 1 and others; logits capped and not; a width that no
+# tensor-core kernel takes.
+FIGALIX_A = dict(seed=31, architecture="Figalix", vocab=96, width=64, norm={"eps": 1e-5}, residual_mult=0.5, logit_softcap=8.0,
+                 layers=[_ssd(heads=4, vdim=8, state=12, groups=2, conv=3, norm_groups=4, mlp=_shares(20, 5, 2, 24)),
+                         _side_by_side(_kept_window(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.4, window=7, keep_first=3,
+                                                    rot_dims=8, rot_base=100.0, scaling=(4.0, 16, 4.0, 1.0)),
+                                       heads=2, dim=24, vdim=12, gate_cap=3.0, mlp=None),
+                         _side_by_side(_kept_window(heads=2, kv_heads=1, dim=8, vdim=8, scale=1.0, window=1, keep_first=2,
+                                                    rot_dims=8, rot_base=50.0),
+                                       heads=1, dim=40, vdim=20, gate_cap=30.0, mlp=_dense(40)),
+                         _ssd(heads=3, vdim=20, state=7, groups=3, conv=1, norm_groups=1, mlp=None)])
+FIGALIX_B = dict(seed=32, architecture="Figalix", vocab=200, width=128, norm={"eps": 1e-6}, residual_mult=1.0,
+                 layers=[_side_by_side(_kept_window(heads=3, kv_heads=3, dim=40, vdim=40, scale=0.16, window=70, keep_first=100,
+                                                    rot_dims=40, rot_base=1e4, scaling=(8.0, 64, 8.0, 2.0)),
+                                       heads=3, dim=64, vdim=32, gate_cap=15.0, mlp=_shares(48, 8, 1, 16)),
+                         _ssd(heads=6, vdim=16, state=64, groups=1, conv=4, norm_groups=2, mlp=_dense(100)),
+                         _side_by_side(_kept_window(heads=9, kv_heads=1, dim=20, vdim=12, scale=0.2, window=130, keep_first=0,
+                                                    rot_dims=6, rot_base=1e6),
+                                       heads=2, dim=96, vdim=72, gate_cap=None, mlp=_shares(40, 3, 3))])
+FIGALIX_C = dict(seed=33, architecture="Figalix", vocab=300, width=256, norm={"eps": 1e-6}, residual_mult=0.8, logit_softcap=50.0,
+                 layers=[_side_by_side(_kept_window(heads=8, kv_heads=2, dim=64, vdim=64, scale=0.125, window=100, keep_first=5,
+                                                    rot_dims=32, rot_base=1e6, scaling=(4.0, 256, 16.0, 2.0)),
+                                       heads=2, dim=128, vdim=128, gate_cap=10.0, mlp=_shares(64, 4, 2, 96)),
+                         _ssd(heads=8, vdim=64, state=128, groups=2, conv=4, norm_groups=1, mlp=_shares(64, 16, 1, 32)),
+                         _side_by_side(_kept_window(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, window=33, keep_first=70,
+                                                    rot_dims=128, rot_base=1e4),
+                                       heads=4, dim=32, vdim=64, gate_cap=15.0, mlp=_dense(320)),
+                         _side_by_side(_kept_window(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, window=64, keep_first=None,
+                                                    rot_dims=64, rot_base=1e5, scaling=(2.0, 128, 4.0, 1.0)),
+                                       heads=2, dim=64, vdim=64, gate_cap=20.0, mlp=_shares(96, 6, 3, 64)),
+                         _ssd(heads=4, vdim=32, state=16, groups=4, conv=2, norm_groups=4, mlp=_dense(128))])
+FIGALIX_D = dict(seed=34, architecture="Figalix", vocab=130, width=100, norm={"eps": 1e-6}, residual_mult=0.3, logit_softcap=2.0,
+                 layers=[_side_by_side(_kept_window(heads=16, kv_heads=1, dim=64, vdim=64, scale=0.125, window=50, keep_first=1,
+                                                    rot_dims=64, rot_base=1e4, scaling=(16.0, 32, 2.0, 0.5)),
+                                       heads=1, dim=256, vdim=8, gate_cap=1.0, mlp=_shares(24, 2, 2, 8)),
+                         _ssd(heads=2, vdim=100, state=256, groups=1, conv=7, norm_groups=5, mlp=None),
+                         _side_by_side(_kept_window(heads=2, kv_heads=2, dim=64, vdim=128, scale=0.3, rot_dims=0),
+                                       heads=2, dim=16, vdim=200, gate_cap=15.0, mlp=_shares(8, 9, 4))])
+FIGALIX_CONFIGS = {"FA": FIGALIX_A, "FB": FIGALIX_B, "FC": FIGALIX_C, "FD": FIGALIX_D}
+
+
+def figalix_config(cfg: dict):
+    """(typed configuration, the dict that goes into config.json)."""
+    from rocmforge_b200.config import architecture_for
+    raw = config_dict(cfg)
+    return architecture_for("Figalix").config_cls.from_dict(raw), raw
+
+
+def write_figalix(cfg: dict, folder: str, dtype: str = "float32") -> None:
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import architecture_for
+    c, raw = figalix_config(cfg)
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    rf.write_model_folder(folder, raw, architecture_for("Figalix").build(c).param_specs(), cfg["seed"], dt)

@@ -95,23 +95,18 @@ def window_attention(h, W, pre, m):
 # --------------------------------------------------------------------------- right mixer: matrix memory
 
 def capped(z, cap):
-    return cap * torch.tanh(z / cap)
+    return z if cap is None else cap * torch.tanh(z / cap)
 
 
-def matrix_memory(h, W, pre, m, eps):
-    """S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T with the running maximum m_t = max(f + m_(t-1), i)
-    (m starts at 0), n likewise with k alone, o = S^T q / (max(|n . q|, exp(-m_t)) + 1e-6)."""
-    T = h.shape[0]
-    H, D, DV, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
-    q = (h @ W[pre + "q"].T).reshape(T, H, D) * D ** -0.5
-    k = (h @ W[pre + "k"].T).reshape(T, H, D)
-    v = (h @ W[pre + "v"].T).reshape(T, H, DV)
-    li = capped(h @ W[pre + "i"].T + W[pre + "i.b"], cap)
-    lf = torch.nn.functional.logsigmoid(capped(h @ W[pre + "f"].T + W[pre + "f.b"], cap))
-    S = torch.zeros((H, D, DV), dtype=h.dtype)
-    n = torch.zeros((H, D), dtype=h.dtype)
-    mx = torch.zeros((H,), dtype=h.dtype)
-    o = torch.zeros((T, H, DV), dtype=h.dtype)
+def memory_recurrence(q, k, v, li, lf, S=None, n=None, mx=None):
+    """q, k [T, H, D], v [T, H, DV], log gates li, lf [T, H]; state (S [H, D, DV], n [H, D], m [H]), zeros if not given.
+    Returns (o [T, H, DV], S, n, m)."""
+    T, H, D = q.shape
+    DV = v.shape[2]
+    S = torch.zeros((H, D, DV), dtype=q.dtype) if S is None else S.clone()
+    n = torch.zeros((H, D), dtype=q.dtype) if n is None else n.clone()
+    mx = torch.zeros((H,), dtype=q.dtype) if mx is None else mx.clone()
+    o = torch.zeros((T, H, DV), dtype=q.dtype)
     for t in range(T):
         new = torch.maximum(lf[t] + mx, li[t])
         keep, take = torch.exp(lf[t] + mx - new), torch.exp(li[t] - new)
@@ -120,6 +115,21 @@ def matrix_memory(h, W, pre, m, eps):
         mx = new
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-mx)) + 1e-6
         o[t] = torch.einsum("hdv,hd->hv", S, q[t]) / den[:, None]
+    return o, S, n, mx
+
+
+def matrix_memory(h, W, pre, m, eps):
+    """S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T with the running maximum m_t = max(f + m_(t-1), i)
+    (m starts at 0), n likewise with k alone, o = S^T q / (max(|n . q|, exp(-m_t)) + 1e-6)."""
+    T = h.shape[0]
+    H, D, DV = m["heads"], m["dim"], m["vdim"]
+    cap = float(m["gate_cap"]) if m.get("gate_cap") is not None else None
+    q = (h @ W[pre + "q"].T).reshape(T, H, D) * D ** -0.5
+    k = (h @ W[pre + "k"].T).reshape(T, H, D)
+    v = (h @ W[pre + "v"].T).reshape(T, H, DV)
+    li = capped(h @ W[pre + "i"].T + W[pre + "i.b"], cap)
+    lf = torch.nn.functional.logsigmoid(capped(h @ W[pre + "f"].T + W[pre + "f.b"], cap))
+    o = memory_recurrence(q, k, v, li, lf)[0]
     o = unit_rms(o, eps).reshape(T, H * DV) * W[pre + "norm"]
     return (o * torch.sigmoid(h @ W[pre + "g"].T)) @ W[pre + "o"].T
 
@@ -142,6 +152,20 @@ def short_convolution(x, w, b):
     return out
 
 
+def duality_recurrence(x, B, C, dt, decay, skip, S=None):
+    """x [T, H, DV], B, C [T, G, N], dt, decay [T, H], skip [H]; state S [H, N, DV], zeros if not given.
+    S_t = decay_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + skip x_t.  Returns (y [T, H, DV], S)."""
+    T, H, DV = x.shape
+    G, N = B.shape[1], B.shape[2]
+    S = torch.zeros((H, N, DV), dtype=x.dtype) if S is None else S.clone()
+    y = torch.zeros((T, H, DV), dtype=x.dtype)
+    group = torch.arange(H) // (H // G)
+    for t in range(T):
+        S = decay[t][:, None, None] * S + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
+        y[t] = torch.einsum("hnv,hn->hv", S, C[t][group]) + skip[:, None] * x[t]
+    return y, S
+
+
 def state_space(h, W, pre, m, eps):
     T = h.shape[0]
     H, DV, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
@@ -154,12 +178,7 @@ def state_space(h, W, pre, m, eps):
     C = xbc[:, inner + G * N:].reshape(T, G, N)
     dt = torch.nn.functional.softplus(dt + W[pre + "dt_bias"], threshold=1e9)
     decay = torch.exp(-torch.exp(W[pre + "A_log"]) * dt)                       # [T, H]
-    S = torch.zeros((H, N, DV), dtype=h.dtype)
-    y = torch.zeros((T, H, DV), dtype=h.dtype)
-    group = torch.arange(H) // (H // G)
-    for t in range(T):
-        S = decay[t][:, None, None] * S + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
-        y[t] = torch.einsum("hnv,hn->hv", S, C[t][group]) + W[pre + "D"][:, None] * x[t]
+    y = duality_recurrence(x, B, C, dt, decay, W[pre + "D"])[0]
     y = y.reshape(T, inner) * silu(z)
     parts = int(m["norm_groups"])
     y = unit_rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * W[pre + "norm"]
@@ -227,3 +246,31 @@ def forward(cfg: dict, W: dict, tokens, dtype=torch.float64, forced=None, trace=
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
     return logits, choices
+
+
+class PlainFigalix:
+    """The plain model of a folder's config.json and tensors."""
+
+    def __init__(self, cfg: dict, tensors: dict):
+        self.cfg, self.W = cfg, tensors
+
+    def logits(self, tokens, forced=None, chosen=None, trace=None):
+        """float64 logits [T, vocab].  ``chosen``: a dict that receives, per layer with experts, for every token the
+        plain model's own experts and the margin between the last one taken and the first one left out, as a share of
+        the router logits' spread (infinite where every expert is taken)."""
+        out, choices = forward(self.cfg, self.W, list(tokens), forced=forced, trace=trace)
+        if chosen is not None:
+            for layer, (s, _) in choices.items():
+                top = int(self.cfg["layers"][layer]["mlp"]["router"]["top"])
+                z = torch.log(s)
+                ranked = torch.sort(z, dim=-1, descending=True)
+                rows = []
+                for t in range(z.shape[0]):
+                    own = ranked.indices[t, :top].tolist()
+                    if top == z.shape[1]:
+                        rows.append((own, float("inf")))
+                    else:
+                        spread = float(ranked.values[t, 0] - ranked.values[t, -1])
+                        rows.append((own, float(ranked.values[t, top - 1] - ranked.values[t, top]) / max(spread, 1e-30)))
+                chosen[layer] = rows
+        return out
