@@ -670,6 +670,33 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ x, int x_stride, const
     }
 }
 
+// The same, 16 bytes of a row a thread (W, the rows' strides and, with a gate per element, the gates' stride are whole
+// numbers of such groups; with a gate per head a group lies inside one head).  Every element is formed as above.
+template <typename T, bool PER_ELEMENT>
+__global__ void sigmoid_gate_vec_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride,
+                                        T* __restrict__ out, size_t n_vec, int Wv, int group) {
+    constexpr int V = 16 / sizeof(T);
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_vec; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / Wv;
+        const int c = (int)(idx - t * Wv) * V;
+        alignas(16) T xs[V], gs[V], ys[V];
+        *reinterpret_cast<uint4*>(xs) = *reinterpret_cast<const uint4*>(x + t * x_stride + c);
+        if (PER_ELEMENT) {
+            *reinterpret_cast<uint4*>(gs) = *reinterpret_cast<const uint4*>(gate + t * gate_stride + c);
+#pragma unroll
+            for (int u = 0; u < V; ++u)
+                ys[u] = Cvt<T>::from_f32(Cvt<T>::to_f32(xs[u]) / (1.f + expf(-Cvt<T>::to_f32(gs[u]))));
+        } else {
+            const float d = 1.f + expf(-Cvt<T>::to_f32(gate[t * gate_stride + c / group]));
+#pragma unroll
+            for (int u = 0; u < V; ++u) ys[u] = Cvt<T>::from_f32(Cvt<T>::to_f32(xs[u]) / d);
+        }
+        *reinterpret_cast<uint4*>(out + t * (size_t)(Wv * V) + c) = *reinterpret_cast<const uint4*>(ys);
+    }
+}
+
 // ---------------------------------------------------------------- the 32-bit stream rounded to the compute dtype
 template <typename T>
 __global__ void round_rows_kernel(const float* __restrict__ h, T* __restrict__ out, size_t n) {
@@ -804,6 +831,20 @@ static int launch_sigmoid_gate(const void* x, int x_stride, const void* gate, in
     if (group < 1) return RF_ERR_BAD_ARG;
     const size_t n = (size_t)T_ * W;
     if (n == 0) return 0;
+    constexpr int V = 16 / (int)sizeof(T);
+    auto whole = [](const void* p, int stride) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && stride % V == 0; };
+    if (W % V == 0 && whole(x, x_stride) && whole(out, W) && (group == 1 ? whole(gate, gate_stride) : group % V == 0)) {
+        const size_t n_vec = n / V, vblocks = (n_vec + 255) / 256;
+        const dim3 grid((unsigned)(vblocks > 148 * 16 ? 148 * 16 : vblocks));
+        if (group == 1)
+            rf_launch(sigmoid_gate_vec_kernel<T, true>, grid, dim3(256), 0, st, reinterpret_cast<const T*>(x), x_stride,
+                      reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n_vec, W / V, group);
+        else
+            rf_launch(sigmoid_gate_vec_kernel<T, false>, grid, dim3(256), 0, st, reinterpret_cast<const T*>(x), x_stride,
+                      reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n_vec, W / V, group);
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
     const size_t blocks = (n + 255) / 256;
     rf_launch(sigmoid_gate_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st,
               reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n, W, group);

@@ -55,7 +55,16 @@ mlstm_gates_kernel(const float* __restrict__ z, float* __restrict__ ab, float* _
         __syncthreads();
         if (threadIdx.x == 0) {
             float m = mm[0];
-            for (int i = 0; i < cnt; ++i) { m = fmaxf(lf[i] + m, li[i]); mm[i + 1] = m; }
+            int i = 0;
+            // eight tokens' gates are fetched before their links of the chain, so that the chain waits for no load
+            for (; i + 8 <= cnt; i += 8) {
+                float f[8], g[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { f[u] = lf[i + u]; g[u] = li[i + u]; }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { m = fmaxf(f[u] + m, g[u]); mm[i + u + 1] = m; }
+            }
+            for (; i < cnt; ++i) { m = fmaxf(lf[i] + m, li[i]); mm[i + 1] = m; }
         }
         __syncthreads();
         for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
