@@ -409,6 +409,303 @@ static int launch_prepare(const void* src, int row_stride, int q_col, int k_col,
 }
 
 // dtype: 0 = float32, 1 = bfloat16 (of the projection's output and of v)
+// ---------------------------------------------------------------- prompts: the scalar form in chunks of 64 tokens
+// S_t = a_t S_(t-1) + b_t k_t v_t^T with one (a_t, b_t) per head and token: the same sums in another order, so that a prompt's
+// chunks run side by side instead of token after token.  With t, s inside a chunk of cnt tokens, S0 the state before it,
+// P_t = a_0 ... a_t and w(t, s) = b_s a_(s+1) ... a_t (running products, formed by multiplying on: no logarithm and no
+// quotient, so a decay of exactly 0 or 1 is like any other):
+//   pass 1 (chunks side by side)   L = sum_s w(cnt-1, s) k_s v_s^T   [dim, vdim],  the same sum without v for the
+//                                   normaliser, and the chunk's whole decay P_(cnt-1)
+//   pass 2 (chunk after chunk, element by element)   S0(next) = P_(cnt-1) S0 + L      (L's place in memory becomes S0's)
+//   pass 3 (chunks side by side)   o_t = sum_(s<=t) w(t, s) (q_t . k_s) v_s + P_t S0^T q_t, and for the normaliser
+//                                   n_t . q_t = sum_(s<=t) w(t, s) (q_t . k_s) + P_t n0 . q_t
+// All 32-bit on the CUDA cores.  The chunk table is retention's: first[B+1], then (sequence, first row) per chunk.
+// Differs from the scan by rounding only.
+#define GC 64                 // tokens of a chunk
+#define GC_LD 68              // row stride of the transposed tiles: rows stay 16-byte aligned
+#define GV 64                 // value columns of a block
+
+// grid (chunk, head, ceil(vdim / GV)); 256 threads: thread (ty, tx) owns rows ty * RPT .. + RPT - 1 (RPT = 4, 8, 12 or 16
+// by dim) and columns 4 tx .. 4 tx + 3 of L
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_chunk_state_kernel(const float* __restrict__ k, int qk_heads, int qk_stride, const float* __restrict__ ab,
+                         const T* __restrict__ v, int v_stride, float* __restrict__ LS, float* __restrict__ NL,
+                         float* __restrict__ CD, const int* __restrict__ table, const int* __restrict__ cu_q, int B,
+                         int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float sh[];
+    const int dimP = (dim + 3) & ~3;                  // rows of 16-byte groups
+    float* ks = sh;                                   // [GC][dimP], already times w(cnt-1, s)
+    float* vs = ks + GC * dimP;                       // [GC][GV]
+    float* as = vs + GC * GV;                         // a_s
+    float* ws = as + GC;                              // b_s, then w(cnt-1, s); ws[GC] = the chunk's whole decay
+    pdl_trigger();
+    const int c = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * GV;
+    const int hq = h / (heads / qk_heads);
+    const int b = table[B + 1 + 2 * c], q0 = table[B + 2 + 2 * c];
+    const int row0 = cu_q[b] + q0, cnt = min(GC, cu_q[b + 1] - row0);
+    pdl_wait();
+    if (threadIdx.x < cnt) {
+        const float2 g = *reinterpret_cast<const float2*>(&ab[((size_t)(row0 + threadIdx.x) * heads + h) * 2]);
+        as[threadIdx.x] = g.x;
+        ws[threadIdx.x] = g.y;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float p = 1.f;
+        for (int s = cnt - 1; s >= 0; --s) { ws[s] *= p; p *= as[s]; }
+        ws[GC] = p;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < cnt * dimP; idx += 256) {
+        const int s = idx / dimP, i = idx - s * dimP;
+        ks[idx] = i < dim ? k[(size_t)(row0 + s) * qk_stride + hq * dim + i] * ws[s] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < cnt * GV; idx += 256) {
+        const int s = idx / GV, j = idx - s * GV;
+        vs[idx] = (j0 + j < vdim) ? Cvt<T>::to_f32(v[(size_t)(row0 + s) * v_stride + h * vdim + j0 + j]) : 0.f;
+    }
+    __syncthreads();
+    if (blockIdx.z == 0) {
+        if (threadIdx.x == 0) CD[(size_t)c * heads + h] = ws[GC];
+        if (NL != nullptr)
+            for (int i = threadIdx.x; i < dim; i += 256) {
+                float n = 0.f;
+                for (int s = 0; s < cnt; ++s) n += ks[s * dimP + i];
+                NL[((size_t)c * heads + h) * dim + i] = n;
+            }
+    }
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int groups = (dim + 63) / 64;               // 16-byte groups of rows per thread
+    const int i0 = ty * 4 * groups;
+    float acc[16][4];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) { acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f; }
+    for (int s = 0; s < cnt; ++s) {
+        const float4 vv = *reinterpret_cast<const float4*>(&vs[s * GV + 4 * tx]);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (g < groups && i0 + 4 * g < dimP) {
+                const float4 kk = *reinterpret_cast<const float4*>(&ks[s * dimP + i0 + 4 * g]);
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    acc[4 * g + x][0] = fmaf(kv[x], vv.x, acc[4 * g + x][0]); acc[4 * g + x][1] = fmaf(kv[x], vv.y, acc[4 * g + x][1]);
+                    acc[4 * g + x][2] = fmaf(kv[x], vv.z, acc[4 * g + x][2]); acc[4 * g + x][3] = fmaf(kv[x], vv.w, acc[4 * g + x][3]);
+                }
+            }
+        }
+    }
+    float* out = LS + (((size_t)c * heads + h) * dim) * vdim;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int i = i0 + r;
+        if (r < 4 * groups && i < dim)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + 4 * tx + u < vdim) out[(size_t)i * vdim + j0 + 4 * tx + u] = acc[r][u];
+    }
+}
+
+// grid (sequence, head, blocks over dim * vdim (+ dim with a normaliser)); a thread owns one element of the state (or of
+// the normaliser) through all chunks
+__global__ void __launch_bounds__(256)
+gated_chunk_carry_kernel(float* __restrict__ LS, float* __restrict__ NL, const float* __restrict__ CD, float* __restrict__ state,
+                         float* __restrict__ nstate, const int* __restrict__ table, const int* __restrict__ cu_q,
+                         const int* __restrict__ seq_slot, int heads, int dim, int vdim) {
+    pdl_trigger();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int ne = dim * vdim;
+    if (e >= ne + (nstate != nullptr ? dim : 0)) return;
+    const int c0 = table[b], c1 = table[b + 1];
+    const bool of_n = e >= ne;
+    float* S = of_n ? nstate + ((size_t)seq_slot[b] * heads + h) * dim + (e - ne)
+                    : state + ((size_t)seq_slot[b] * heads + h) * ne + e;
+    const size_t step = (size_t)heads * (of_n ? dim : ne);
+    float* p = of_n ? NL + ((size_t)c0 * heads + h) * dim + (e - ne) : LS + ((size_t)c0 * heads + h) * ne + e;
+    const float* cd = CD + (size_t)c0 * heads + h;
+    pdl_wait();
+    float s = *S;
+    for (int c = c0; c < c1; c += 8) {                   // eight chunks' sums on their way at once; the chain is the FMAs alone
+        float l[8], d[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            l[u] = (c + u < c1) ? p[(size_t)u * step] : 0.f;
+            d[u] = (c + u < c1) ? cd[(size_t)u * heads] : 1.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (c + u < c1) {
+                p[(size_t)u * step] = s;                 // the state before chunk c + u
+                s = fmaf(d[u], s, l[u]);
+            }
+        p += 8 * step;
+        cd += 8 * (size_t)heads;
+    }
+    *S = s;
+}
+
+// grid (chunk, head, ceil(vdim / GV)); 256 threads as a 16 x 16 grid of 4 x 4 tiles
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_chunk_out_kernel(const float* __restrict__ q, const float* __restrict__ k, int qk_heads, int qk_stride,
+                       const float* __restrict__ ab, const T* __restrict__ v, int v_stride, const float* __restrict__ LS,
+                       const float* __restrict__ NL, float* __restrict__ o, float* __restrict__ qn,
+                       const int* __restrict__ table, const int* __restrict__ cu_q, int B, int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float sh[];
+    float* qt = sh;                                   // [dim][GC_LD]: q transposed
+    float* kt = qt + dim * GC_LD;                     // [dim][GC_LD]: k transposed; later the state S0 as [dim][GV]
+    float* vs = kt + dim * GC_LD;                     // [GC][GV]
+    float* at = vs + GC * GV;                         // [GC (s)][GC_LD (t)]: w(t, s), then the weighted scores, transposed
+    float* as = at + GC * GC_LD;                      // a_t
+    float* bs = as + GC;                              // b_s
+    float* pt = bs + GC;                              // P_t
+    pdl_trigger();
+    const int c = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * GV;
+    const int hq = h / (heads / qk_heads);
+    const int b = table[B + 1 + 2 * c], q0 = table[B + 2 + 2 * c];
+    const int row0 = cu_q[b] + q0, cnt = min(GC, cu_q[b + 1] - row0);
+    pdl_wait();
+    if (threadIdx.x < GC) {
+        float2 g = make_float2(1.f, 0.f);
+        if (threadIdx.x < cnt) g = *reinterpret_cast<const float2*>(&ab[((size_t)(row0 + threadIdx.x) * heads + h) * 2]);
+        as[threadIdx.x] = g.x;
+        bs[threadIdx.x] = g.y;
+    }
+    for (int idx = threadIdx.x; idx < GC * dim; idx += 256) {
+        const int s = idx / dim, i = idx - s * dim;
+        const bool in = s < cnt;
+        qt[i * GC_LD + s] = in ? q[(size_t)(row0 + s) * qk_stride + hq * dim + i] : 0.f;
+        kt[i * GC_LD + s] = in ? k[(size_t)(row0 + s) * qk_stride + hq * dim + i] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < GC * GV; idx += 256) {
+        const int s = idx / GV, j = idx - s * GV;
+        vs[idx] = (s < cnt && j0 + j < vdim) ? Cvt<T>::to_f32(v[(size_t)(row0 + s) * v_stride + h * vdim + j0 + j]) : 0.f;
+    }
+    __syncthreads();
+    // the running products: thread s multiplies b_s on by a_(s+1), a_(s+2), ...; one more thread forms P_t
+    if (threadIdx.x < GC) {
+        const int s = threadIdx.x;
+        float run = bs[s];
+        at[s * GC_LD + s] = run;
+        for (int t = s + 1; t < GC; ++t) { run *= as[t]; at[s * GC_LD + t] = run; }
+    } else if (threadIdx.x == GC) {
+        float p = 1.f;
+        for (int t = 0; t < GC; ++t) { p *= as[t]; pt[t] = p; }
+    }
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;        // rows (t) 4 ty .., columns 4 tx ..
+    float a[4][4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) { a[x][0] = a[x][1] = a[x][2] = a[x][3] = 0.f; }
+    if (tx <= ty) {                                      // tiles above the diagonal are zero
+        for (int i = 0; i < dim; ++i) {
+            const float4 qq = *reinterpret_cast<const float4*>(&qt[i * GC_LD + 4 * ty]);
+            const float4 kk = *reinterpret_cast<const float4*>(&kt[i * GC_LD + 4 * tx]);
+            const float qv[4] = {qq.x, qq.y, qq.z, qq.w}, kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y) a[x][y] = fmaf(qv[x], kv[y], a[x][y]);
+        }
+    }
+    __syncthreads();                                     // the products are in place; k is used up
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+            const int t = 4 * ty + x, s = 4 * tx + y;
+            at[s * GC_LD + t] = (s <= t) ? a[x][y] * at[s * GC_LD + t] : 0.f;
+        }
+    const float* S0 = LS + (((size_t)c * heads + h) * dim) * vdim;
+    for (int idx = threadIdx.x; idx < dim * GV; idx += 256) {
+        const int i = idx / GV, j = idx - i * GV;
+        kt[idx] = (j0 + j < vdim) ? S0[(size_t)i * vdim + j0 + j] : 0.f;
+    }
+    __syncthreads();
+    if (qn != nullptr && blockIdx.z == 0 && threadIdx.x < cnt) {
+        const int t = threadIdx.x;
+        const float* n0 = NL + ((size_t)c * heads + h) * dim;
+        float inside = 0.f, before = 0.f;
+        for (int s = 0; s <= t; ++s) inside += at[s * GC_LD + t];
+        for (int i = 0; i < dim; ++i) before = fmaf(qt[i * GC_LD + t], n0[i], before);
+        qn[(size_t)(row0 + t) * heads + h] = fmaf(pt[t], before, inside);
+    }
+    float o1[4][4], o2[4][4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) { o1[x][y] = 0.f; o2[x][y] = 0.f; }
+    const int s_end = min(cnt, 4 * ty + 4);              // later keys have zero scores for these rows
+    for (int s = 0; s < s_end; ++s) {
+        const float4 aa = *reinterpret_cast<const float4*>(&at[s * GC_LD + 4 * ty]);
+        const float4 vv = *reinterpret_cast<const float4*>(&vs[s * GV + 4 * tx]);
+        const float av[4] = {aa.x, aa.y, aa.z, aa.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) o1[x][y] = fmaf(av[x], vw[y], o1[x][y]);
+    }
+    for (int i = 0; i < dim; ++i) {
+        const float4 qq = *reinterpret_cast<const float4*>(&qt[i * GC_LD + 4 * ty]);
+        const float4 ss = *reinterpret_cast<const float4*>(&kt[i * GV + 4 * tx]);
+        const float qv[4] = {qq.x, qq.y, qq.z, qq.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) o2[x][y] = fmaf(qv[x], sv[y], o2[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int t = 4 * ty + x;
+        if (t < cnt)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+                const int j = j0 + 4 * tx + y;
+                if (j < vdim) o[(size_t)(row0 + t) * heads * vdim + h * vdim + j] = fmaf(pt[t], o2[x][y], o1[x][y]);
+            }
+    }
+}
+
+template <typename T>
+static int launch_gated_chunked(const float* q, const float* k, int qk_heads, int qk_stride, const float* ab, const void* v,
+                                int v_stride, float* state, float* nstate, float* o, float* qn, float* scratch,
+                                const int* table, int n_chunks, const int* cu_q, const int* seq_slot, int B, int heads,
+                                int dim, int vdim, cudaStream_t st) {
+    if (B <= 0 || n_chunks <= 0) return 0;
+    if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535 || B > 65535 || qk_heads <= 0 || heads % qk_heads)
+        return RF_ERR_UNSUPPORTED;
+    if ((nstate == nullptr) != (qn == nullptr)) return RF_ERR_BAD_ARG;
+    float* LS = scratch;                                           // [n_chunks, heads, dim, vdim]
+    float* CD = LS + (size_t)n_chunks * heads * dim * vdim;        // [n_chunks, heads]
+    float* NL = nstate != nullptr ? CD + (size_t)n_chunks * heads : nullptr;   // [n_chunks, heads, dim]
+    const int vz = (vdim + GV - 1) / GV;
+    const size_t smem1 = (size_t)(GC * ((dim + 3) & ~3) + GC * GV + 2 * GC + 4) * sizeof(float);
+    const size_t smem3 = (size_t)(2 * dim * GC_LD + GC * GV + GC * GC_LD + 3 * GC) * sizeof(float);
+    static size_t set1 = 48 * 1024, set3 = 48 * 1024;
+    if (smem1 > set1) {
+        cudaError_t e = cudaFuncSetAttribute(gated_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+        if (e != cudaSuccess) return (int)e;
+        set1 = smem1;
+    }
+    if (smem3 > set3) {
+        cudaError_t e = cudaFuncSetAttribute(gated_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+        if (e != cudaSuccess) return (int)e;
+        set3 = smem3;
+    }
+    rf_launch(gated_chunk_state_kernel<T>, dim3(n_chunks, heads, vz), dim3(256), smem1, st, k, qk_heads, qk_stride, ab,
+              reinterpret_cast<const T*>(v), v_stride, LS, NL, CD, table, cu_q, B, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    const int elements = dim * vdim + (nstate != nullptr ? dim : 0);
+    rf_launch(gated_chunk_carry_kernel, dim3(B, heads, (elements + 255) / 256), dim3(256), 0, st, LS, NL, (const float*)CD, state,
+              nstate, table, cu_q, seq_slot, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    rf_launch(gated_chunk_out_kernel<T>, dim3(n_chunks, heads, vz), dim3(256), smem3, st, q, k, qk_heads, qk_stride, ab,
+              reinterpret_cast<const T*>(v), v_stride, (const float*)LS, (const float*)NL, o, qn, table, cu_q, B, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 extern "C" {
 // src [T, row_stride]: q at columns q_col.., k at k_col.. (width = heads*dim each); z float [T, width]; qka float [3, T, width]
 int rf_gla_prepare(int dtype, const void* src, int row_stride, int q_col, int k_col, const float* z, float* qka, int width,
@@ -436,5 +733,16 @@ int rf_gated_scan(int dtype, const float* q, const float* k, int qk_heads, int q
     const ScalarArgs x = {qk_heads, qk_stride, nstate, qn};
     return dtype == 0 ? launch_scan<float, true>(q, k, ab, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st)
                       : launch_scan<__nv_bfloat16, true>(q, k, ab, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, x, st);
+}
+// The scalar recurrence of a prompt step in chunks of 64 tokens (see above).  scratch: float, n_chunks * heads *
+// (dim * vdim + 1 (+ dim with a normaliser)); table: first[B+1], then n_chunks pairs (sequence, first row of the chunk among
+// the sequence's new tokens).  The other arguments are rf_gated_scan's.
+int rf_gated_chunked(int dtype, const float* q, const float* k, int qk_heads, int qk_stride, const float* ab, const void* v,
+                     int v_stride, float* state, float* nstate, float* o, float* qn, float* scratch, const int* table,
+                     int n_chunks, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, cudaStream_t st) {
+    return dtype == 0 ? launch_gated_chunked<float>(q, k, qk_heads, qk_stride, ab, v, v_stride, state, nstate, o, qn, scratch, table,
+                                                    n_chunks, cu_q, seq_slot, B, heads, dim, vdim, st)
+                      : launch_gated_chunked<__nv_bfloat16>(q, k, qk_heads, qk_stride, ab, v, v_stride, state, nstate, o, qn, scratch,
+                                                            table, n_chunks, cu_q, seq_slot, B, heads, dim, vdim, st);
 }
 }

@@ -1030,6 +1030,42 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, ab: torch.Tensor, v: torch.Tens
     return o, qn
 
 
+def gated_chunked(q: torch.Tensor, k: torch.Tensor, ab: torch.Tensor, v: torch.Tensor, state: torch.Tensor, table: torch.Tensor,
+                  cu_q: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int, *, qk_heads: int | None = None,
+                  nstate: torch.Tensor | None = None):
+    """What ``gated_scan`` computes, for prompts: the recurrence in chunks of 64 tokens that run side by side (per-chunk
+    sums weighted by running products of the decays, then the states between the chunks one after the other, then every
+    chunk's outputs from its start state), all in 32-bit.  ``table``: the chunk table of ``retention_chunked``.  The other
+    arguments and the results are ``gated_scan``'s.  Differs from the scan by rounding only."""
+    need_cuda(q, k, ab, v, state, table, cu_q, seq_slot, nstate)
+    T = ab.shape[0]
+    B = seq_slot.shape[0]
+    qk_heads = heads if qk_heads is None else int(qk_heads)
+    need(heads % qk_heads == 0, "gated_chunked: the heads must share q and k heads evenly")
+    for x in (q, k):
+        need(x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] == T and x.shape[1] >= qk_heads * dim and x.stride(1) == 1
+             and x.stride(0) == q.stride(0), "gated_chunked: q and k must be float32 [T, >= qk_heads*dim] with one row stride")
+    need(ab.dtype == torch.float32 and ab.is_contiguous() and ab.shape == (T, heads, 2), "gated_chunked: ab must be float32 [T, heads, 2]")
+    need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "gated_chunked: v must be [T, heads*vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+         "gated_chunked: state must be float32 [slots, heads, dim, vdim]")
+    need(nstate is None or (nstate.dtype == torch.float32 and nstate.is_contiguous() and tuple(nstate.shape[1:]) == (heads, dim)),
+         "gated_chunked: the normaliser's state must be float32 [slots, heads, dim]")
+    need(table.dtype == torch.int32 and (table.numel() - (B + 1)) % 2 == 0 and table.numel() > B + 1,
+         "gated_chunked: the chunk table must hold first[B+1] and a pair per chunk")
+    n_chunks = (table.numel() - (B + 1)) // 2
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=ab.device)
+    qn = torch.empty((T, heads), dtype=torch.float32, device=ab.device) if nstate is not None else None
+    scratch = torch.empty((n_chunks * heads * (dim * vdim + 1 + (dim if nstate is not None else 0)),), dtype=torch.float32,
+                          device=ab.device)
+    f = _f("gla", "rf_gated_chunked", c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(v.dtype), ptr(q), ptr(k), qk_heads, q.stride(0), ptr(ab), ptr(v), v.stride(0), ptr(state), ptr(nstate),
+            ptr(o), ptr(qn), ptr(scratch), ptr(table), n_chunks, ptr(cu_q), ptr(seq_slot), B, heads, dim, vdim, stream()),
+          f"gated_chunked (heads={heads}, dim={dim}, vdim={vdim})")
+    return o, qn
+
+
 # ---------------------------------------------------------------- matrix memory (csrc/mlstm.cu)
 
 def mlstm_prepare(proj: torch.Tensor, q_col: int, k_col: int, width: int, q_scale: float) -> torch.Tensor:

@@ -12,6 +12,7 @@ from ..engine.stream import ScaledRows
 from ..weights.spec import ParamSpec
 from .base import MIXERS, Mixer
 from .linear import Linear
+from .retention import recurrence_chunk_table
 
 
 @MIXERS.register("mamba2")
@@ -90,6 +91,15 @@ class StateSpaceDuality(Mixer):
     def cuda_modules(self, compute_dtype):
         return ["elementwise", "gla", "mamba2"]
 
+    # Prompts run the recurrence in chunks side by side; steps of few tokens per sequence run it token by token.
+    CHUNKED_FROM = 17            # tokens of the step's longest portion from which the chunked kernels are taken
+
+    def step_table_names(self):
+        return ("retention_chunks",)
+
+    def step_table(self, name, batch):
+        return recurrence_chunk_table(batch, self.CHUNKED_FROM)
+
     def cache_request(self):
         named = dict(S=((self.n_heads, self.state, self.vdim), torch.float32))
         if self.taps > 1:
@@ -114,8 +124,13 @@ class StateSpaceDuality(Mixer):
         u = ubc[:, :self.inner]
         b = ubc[:, self.inner:self.inner + self.bc]
         c = ubc[:, self.inner + self.bc:]
-        s, _ = kernels.gated_scan(c, b, ab, u, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.state,
-                                  self.vdim, qk_heads=self.groups, one_token=ctx.is_decode)
+        table = ctx.tables.get("retention_chunks")
+        if table is not None and table.numel() > 0:
+            s, _ = kernels.gated_chunked(c, b, ab, u, state_view["S"], table, ctx.cu_q, ctx.seq_slot, self.n_heads, self.state,
+                                         self.vdim, qk_heads=self.groups)
+        else:
+            s, _ = kernels.gated_scan(c, b, ab, u, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.state,
+                                      self.vdim, qk_heads=self.groups, one_token=ctx.is_decode)
         return kernels.mamba_finish(s, u, p[:, :self.inner], self.skip, self.norm_w, self.norm_groups, self.vdim, self.eps)
 
     def forward(self, ctx, y, cache_view, stream):

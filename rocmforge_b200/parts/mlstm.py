@@ -12,6 +12,7 @@ from ..engine.stream import ScaledRows
 from ..weights.spec import ParamSpec
 from .base import MIXERS, Mixer
 from .linear import Linear
+from .retention import recurrence_chunk_table
 
 
 @MIXERS.register("mlstm")
@@ -76,6 +77,15 @@ class MatrixMemory(Mixer):
     def cuda_modules(self, compute_dtype):
         return ["elementwise", "retention", "gla", "mlstm"]
 
+    # Prompts run the recurrence in chunks side by side; steps of few tokens per sequence run it token by token.
+    CHUNKED_FROM = 17            # tokens of the step's longest portion from which the chunked kernels are taken
+
+    def step_table_names(self):
+        return ("retention_chunks",)
+
+    def step_table(self, name, batch):
+        return recurrence_chunk_table(batch, self.CHUNKED_FROM)
+
     def cache_request(self):
         return StateRequest.of(S=((self.n_heads, self.dim, self.vdim), torch.float32),
                                n=((self.n_heads, self.dim), torch.float32), m=((self.n_heads,), torch.float32))
@@ -91,8 +101,13 @@ class MatrixMemory(Mixer):
                                      ctx.max_new)
         v = p[:, 2 * self.qk_size: 2 * self.qk_size + self.v_size]
         g = p[:, 2 * self.qk_size + self.v_size: 2 * self.qk_size + 2 * self.v_size]
-        o, qn = kernels.gated_scan(qk[0], qk[1], ab, v, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.dim,
-                                   self.vdim, nstate=state_view["n"], one_token=ctx.is_decode)
+        table = ctx.tables.get("retention_chunks")
+        if table is not None and table.numel() > 0:
+            o, qn = kernels.gated_chunked(qk[0], qk[1], ab, v, state_view["S"], table, ctx.cu_q, ctx.seq_slot, self.n_heads,
+                                          self.dim, self.vdim, nstate=state_view["n"])
+        else:
+            o, qn = kernels.gated_scan(qk[0], qk[1], ab, v, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.dim,
+                                       self.vdim, nstate=state_view["n"], one_token=ctx.is_decode)
         return kernels.retention_gate(o, g, self.n_heads, self.vdim, self.eps, weight=self.norm_w, gate_fn="sigmoid",
                                       denominator=(qn, mt))
 

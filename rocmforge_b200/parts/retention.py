@@ -14,6 +14,19 @@ from .base import MIXERS, Mixer
 from .linear import Linear
 
 
+def recurrence_chunk_table(batch, chunked_from: int) -> np.ndarray:
+    """The table of the recurrences' chunked kernels: first[B+1] (index of each sequence's first chunk), then (sequence,
+    first row) of every chunk of 64 new tokens; empty for steps that take the token-by-token kernel (decoding, and
+    portions whose longest is below ``chunked_from`` tokens)."""
+    if batch.is_decode or batch.max_new < chunked_from:
+        return np.zeros((0,), dtype=np.int32)
+    C = kernels.RETENTION_CHUNK
+    counts = [(int(n) + C - 1) // C for n in batch.n_new]
+    first = np.concatenate([[0], np.cumsum(counts)])
+    pairs = [(b, q0) for b in range(batch.B) for q0 in range(0, int(batch.n_new[b]), C)]
+    return np.concatenate([first, np.asarray(pairs, dtype=np.int64).reshape(-1)]).astype(np.int32)
+
+
 @MIXERS.register("retention")
 class Retention(Mixer):
     """Per head, with q, k of size ``dim`` and v of size ``vdim``:
@@ -73,15 +86,7 @@ class Retention(Mixer):
         return ("retention_chunks",)
 
     def step_table(self, name, batch):
-        """first[B+1] (index of each sequence's first chunk), then (sequence, first row) of every chunk of 64 new tokens;
-        empty for steps that take the token-by-token kernel."""
-        if batch.is_decode or batch.max_new < self.CHUNKED_FROM:
-            return np.zeros((0,), dtype=np.int32)
-        C = kernels.RETENTION_CHUNK
-        counts = [(int(n) + C - 1) // C for n in batch.n_new]
-        first = np.concatenate([[0], np.cumsum(counts)])
-        pairs = [(b, q0) for b in range(batch.B) for q0 in range(0, int(batch.n_new[b]), C)]
-        return np.concatenate([first, np.asarray(pairs, dtype=np.int64).reshape(-1)]).astype(np.int32)
+        return recurrence_chunk_table(batch, self.CHUNKED_FROM)
 
     def gated(self, ctx, y, state_view):
         """The gated, normed heads [T, heads*vdim] in the compute dtype (the output product's input)."""

@@ -527,6 +527,24 @@ def _steps(lengths_per_step):
     return out
 
 
+def _chunk_table(step):
+    """first[B+1], then (sequence, first row) of every chunk of 64 of a step's new tokens."""
+    first, pairs = [0], []
+    for b, (_, n) in enumerate(step):
+        first.append(first[-1] + (n + 63) // 64)
+        pairs += [(b, r) for r in range(0, n, 64)]
+    return torch.tensor(first + [x for pair in pairs for x in pair], dtype=torch.int32, device="cuda")
+
+
+def _recurrence(form, step, q, k, ab, v, S, cu, slots, heads, dim, vdim, **kw):
+    """The scalar recurrence by the kernel that runs token by token, or (``form`` "chunks", steps with a portion of more
+    than one token) by the chunked kernels."""
+    from rocmforge_b200 import kernels
+    if form == "chunks" and any(c > 1 for _, c in step):
+        return kernels.gated_chunked(q, k, ab, v, S, _chunk_table(step), cu, slots, heads, dim, vdim, **kw)
+    return kernels.gated_scan(q, k, ab, v, S, cu, slots, heads, dim, vdim, one_token=all(c == 1 for _, c in step), **kw)
+
+
 # two sequences in slots 2 and 0 of 3: a prompt step of unequal portions, a second portion (one of them of 2 tokens),
 # then two single-token steps
 MEMORY_STEPS = [[(2, 37), (0, 5)], [(2, 2), (0, 70)], [(2, 1), (0, 1)], [(2, 1), (0, 1)]]
@@ -534,7 +552,8 @@ MEMORY_STEPS = [[(2, 37), (0, 5)], [(2, 2), (0, 70)], [(2, 1), (0, 1)], [(2, 1),
 
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 24, 12, 3.0), (1, 40, 20, None), (3, 64, 32, 15.0), (2, 128, 128, 1.0),
                                                  (1, 256, 8, 30.0), (2, 16, 200, 15.0)])
-def test_matrix_memory_kernels(heads, dim, vdim, cap):
+@pytest.mark.parametrize("form", ["scan", "chunks"])
+def test_matrix_memory_kernels(heads, dim, vdim, cap, form):
     """The gates' chain, the recurrence with its normaliser and the division, against the plain recurrence: states carried
     over steps in slots of their own, sizes that are no multiple of a warp's rows, capped and uncapped gates.  The first
     sequence's input gates are all far below zero, so that its running maximum is what the forget gates leave of the
@@ -565,9 +584,8 @@ def test_matrix_memory_kernels(heads, dim, vdim, cap):
         T = rows["q"].shape[0]
         z = torch.cat([rows["zi"], rows["zf"]], dim=1).contiguous()
         ab, mt = kernels.mlstm_gates(z, m, cu, slots, heads, cap or 0.0, max(c for _, c in step))
-        o, qn = kernels.gated_scan(rows["q"].reshape(T, -1).contiguous(), rows["k"].reshape(T, -1).contiguous(), ab,
-                                   rows["v"].reshape(T, -1).contiguous(), S, cu, slots, heads, dim, vdim, nstate=n,
-                                   one_token=all(c == 1 for _, c in step))
+        o, qn = _recurrence(form, step, rows["q"].reshape(T, -1).contiguous(), rows["k"].reshape(T, -1).contiguous(), ab,
+                            rows["v"].reshape(T, -1).contiguous(), S, cu, slots, heads, dim, vdim, nstate=n)
         den = torch.maximum(qn.abs(), torch.exp(-mt)) + 1e-6
         o = (o.reshape(T, heads, vdim) / den[:, :, None]).cpu()
         r = 0
@@ -581,6 +599,69 @@ def test_matrix_memory_kernels(heads, dim, vdim, cap):
         assert (n[slot].cpu().double() - n_want).abs().max() < 2e-4 * max(1.0, float(n_want.abs().max()))
         assert (m[slot].cpu().double() - m_want).abs().max() < 1e-5
     assert torch.isnan(S[1]).all() and torch.isnan(m[1]).all()      # the slot of no sequence was not touched
+
+
+@pytest.mark.parametrize("dim,vdim,qk_heads", [(16, 8, 2), (128, 128, 1), (40, 70, 2)])
+def test_chunked_recurrence_at_its_edges(dim, vdim, qk_heads):
+    """The chunked kernels against the recurrence written out, where random gates would hide a fault.  Head 0 never forgets
+    (decay exactly 1) and takes in one early token only, so every later output is that token's value times q . k, across
+    every chunk border and the border between two steps.  Head 1 forgets everything (decay exactly 0) at the first and at
+    the last token of a chunk and in the middle of one, so nothing older may show after these.  The sequences' lengths
+    leave chunks of one token, of 63, 64 and 65 tokens."""
+    from rocmforge_b200 import kernels
+    torch.manual_seed(dim)
+    heads = 2
+    steps = [[(1, 193), (0, 63)], [(1, 65), (0, 64)], [(1, 1), (0, 1)]]
+    totals = {1: 259, 0: 128}
+    data = {}
+    for slot, T in totals.items():
+        a = torch.rand(T, heads) * 0.5 + 0.5
+        b = torch.rand(T, heads)
+        a[:, 0] = 1.0
+        b[:, 0] = 0.0
+        b[3, 0] = 1.0
+        for t in (64, 127, 100, 192, 193):
+            if t < T:
+                a[t, 1] = 0.0
+        data[slot] = dict(q=torch.randn(T, qk_heads, dim) * dim ** -0.5, k=torch.randn(T, qk_heads, dim), v=torch.randn(T, heads, vdim),
+                          ab=torch.stack([a, b], dim=2))
+    want = {}
+    for slot, d in data.items():
+        T = totals[slot]
+        S = torch.zeros(heads, dim, vdim, dtype=torch.float64)
+        nn_ = torch.zeros(heads, dim, dtype=torch.float64)
+        o = torch.zeros(T, heads, vdim, dtype=torch.float64)
+        qn = torch.zeros(T, heads, dtype=torch.float64)
+        for t in range(T):
+            for h in range(heads):
+                g = h // (heads // qk_heads)
+                a, b = d["ab"][t, h].double()
+                S[h] = a * S[h] + b * torch.outer(d["k"][t, g].double(), d["v"][t, h].double())
+                nn_[h] = a * nn_[h] + b * d["k"][t, g].double()
+                o[t, h] = S[h].T @ d["q"][t, g].double()
+                qn[t, h] = nn_[h] @ d["q"][t, g].double()
+        want[slot] = (o, qn, S.clone(), nn_.clone())
+        o3 = torch.einsum("td,d->t", d["q"][:, 0].double(), d["k"][3, 0].double())[:, None] * d["v"][3, 0].double()
+        assert (o[3:, 0] - o3[3:]).abs().max() < 1e-9          # the plain loop itself keeps the early token for ever
+    S = torch.full((2, heads, dim, vdim), 0.0, device="cuda")
+    n = torch.full((2, heads, dim), 0.0, device="cuda")
+    at = {1: 0, 0: 0}
+    got_o, got_n = {1: [], 0: []}, {1: [], 0: []}
+    for (cu, slots, _), step in zip(_steps(steps), steps):
+        rows = {k: torch.cat([data[s][k][at[s]: at[s] + c] for s, c in step]).cuda() for k in ("q", "k", "v", "ab")}
+        T = rows["q"].shape[0]
+        o, qn = _recurrence("chunks", step, rows["q"].reshape(T, -1).contiguous(), rows["k"].reshape(T, -1).contiguous(),
+                            rows["ab"].contiguous(), rows["v"].reshape(T, -1).contiguous(), S, cu, slots, heads, dim, vdim,
+                            qk_heads=qk_heads, nstate=n)
+        r = 0
+        for s, c in step:
+            got_o[s].append(o[r: r + c].cpu().reshape(c, heads, vdim)); got_n[s].append(qn[r: r + c].cpu()); r += c; at[s] += c
+    for slot in totals:
+        o_want, qn_want, S_want, n_want = want[slot]
+        assert (torch.cat(got_o[slot]).double() - o_want).abs().max() < 1e-4 * max(1.0, float(o_want.abs().max())), f"slot {slot}"
+        assert (torch.cat(got_n[slot]).double() - qn_want).abs().max() < 1e-4 * max(1.0, float(qn_want.abs().max()))
+        assert (S[slot].cpu().double() - S_want).abs().max() < 1e-4 * max(1.0, float(S_want.abs().max()))
+        assert (n[slot].cpu().double() - n_want).abs().max() < 1e-4 * max(1.0, float(n_want.abs().max()))
 
 
 def test_matrix_memory_norm_and_gate():
@@ -603,7 +684,8 @@ def test_matrix_memory_norm_and_gate():
 
 @pytest.mark.parametrize("heads,vdim,state,groups,taps,parts", [(4, 8, 12, 2, 3, 4), (3, 20, 7, 3, 1, 1), (6, 16, 64, 1, 4, 2),
                                                                  (2, 100, 256, 1, 7, 5), (8, 64, 128, 2, 4, 1)])
-def test_state_space_kernels(heads, vdim, state, groups, taps, parts):
+@pytest.mark.parametrize("form", ["scan", "chunks"])
+def test_state_space_kernels(heads, vdim, state, groups, taps, parts, form):
     """The short convolution with its carried inputs (a portion shorter than the taps among the steps), the step sizes
     without a clamp (pre-activations up to 40), the recurrence with heads that share a group's B and C, the skip, the
     gate before the norm and the norm in parts, against the plain functions."""
@@ -642,8 +724,8 @@ def test_state_space_kernels(heads, vdim, state, groups, taps, parts):
         rows = {k: torch.cat([data[s][k][at[s]: at[s] + c] for s, c in step]).cuda().contiguous() for k in ("xbc", "zdt", "gate")}
         u = kernels.conv_silu(rows["xbc"], 0, C, conv, dev["w"], dev["bias"], tok_seq, cu, slots)
         ab = kernels.mamba_gates(rows["zdt"], dev["dt_bias"], dev["a_log"])
-        y, _ = kernels.gated_scan(u[:, inner + bc:], u[:, inner: inner + bc], ab, u[:, :inner], S, cu, slots, heads, state, vdim,
-                                  qk_heads=groups, one_token=all(c == 1 for _, c in step))
+        y, _ = _recurrence(form, step, u[:, inner + bc:], u[:, inner: inner + bc], ab, u[:, :inner], S, cu, slots, heads, state,
+                           vdim, qk_heads=groups)
         out = kernels.mamba_finish(y, u[:, :inner], rows["gate"], dev["skip"], dev["norm_w"], parts, vdim, eps)
         r = 0
         for s, c in step:
