@@ -46,7 +46,8 @@ class KVGroup:
         # [owner, k|v, page, kv_head, position in page, head_dim]; values of another head size than keys have a tensor
         # of their own (storage then holds the keys alone)
         self.separate_values = request.v_head_dim is not None and request.v_head_dim != request.head_dim
-        self.storage = torch.zeros((len(self.owners), 1 if self.separate_values else 2, n_pages, request.n_kv_heads, PAGE,
+        self.keys_only = bool(request.values_are_keys)             # the values are the keys: one plane, read twice
+        self.storage = torch.zeros((len(self.owners), 1 if self.separate_values or self.keys_only else 2, n_pages, request.n_kv_heads, PAGE,
                                     request.head_dim), dtype=dtype, device=device)
         self.value_storage = (torch.zeros((len(self.owners), 1, n_pages, request.n_kv_heads, PAGE, request.v_head_dim),
                                           dtype=dtype, device=device) if self.separate_values else None)
@@ -152,7 +153,7 @@ class KVGroup:
     def v_pages(self, owner: int) -> torch.Tensor:
         if self.separate_values:
             return self.value_storage[self.index_of[owner], 0]
-        return self.storage[self.index_of[owner], 1]
+        return self.storage[self.index_of[owner], 0 if self.keys_only else 1]
 
 
 @dataclass

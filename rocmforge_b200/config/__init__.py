@@ -5,4 +5,5 @@ from .qwen2 import Qwen2Config
 from .rifizen import RifizenConfig
 from .vilulorn import VilulornConfig
 from .figalix import FigalixConfig
+from .ludusun import LudusunConfig
 from . import vilulorn   # (its builder registers "Vilulorn")

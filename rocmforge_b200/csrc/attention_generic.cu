@@ -41,7 +41,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ seq_slot, const int* __restrict__ block_table,
                          int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                         const float* __restrict__ slopes, int window, int hpb, int keep_first) {
+                         const float* __restrict__ slopes, int window, int hpb, int keep_first,
+                         const float* __restrict__ sinks) {
     constexpr int ACC = ATT_GB * (CK == 128 ? 256 : ATT_MAX_HD) / ATT_THREADS;     // (head, dim) pairs of a thread at most
     pdl_trigger();
     pdl_wait();
@@ -202,6 +203,19 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 }
             }
         }
+        // a sink per head: one more term exp(sink) in the softmax's denominator that has no key and no value (it is
+        // not scaled); folded in as if it were a last key whose value is zero
+        float sink_corr[ATT_GB];
+#pragma unroll
+        for (int g = 0; g < ATT_GB; ++g) {
+            sink_corr[g] = 1.f;
+            if (sinks != nullptr && g < gb) {
+                const float sk = sinks[kvh * G + g0 + g];
+                const float m_new = fmaxf(m_run[g], sk);
+                sink_corr[g] = (m_run[g] == -INFINITY) ? 0.f : expf(m_run[g] - m_new);
+                l_run[g] = l_run[g] * sink_corr[g] + expf(sk - m_new);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < ACC; ++i) {
             const int e = tid + i * ATT_THREADS;
@@ -209,7 +223,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 const int g = e / hdv, d = e - g * hdv;
                 float l = 0.f;
 #pragma unroll
-                for (int gg = 0; gg < ATT_GB; ++gg) if (gg == g) l = l_run[gg];
+                for (int gg = 0; gg < ATT_GB; ++gg) if (gg == g) { l = l_run[gg]; acc[i] *= sink_corr[gg]; }
                 out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * hdv + d] = Cvt<T>::from_f32(l > 0.f ? acc[i] / l : 0.f);
             }
         }
@@ -220,7 +234,7 @@ template <typename T, int CK>
 static int launch_ck(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                      const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                      const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                     const float* slopes, int window, int T_, cudaStream_t st, int keep_first) {
+                     const float* slopes, int window, int T_, cudaStream_t st, int keep_first, const float* sinks) {
     const int hm = hd > hdv ? hd : hdv;
     const size_t smem = ((size_t)ATT_GB * hd + (size_t)CK * (hm + 1) + ATT_GB * CK + ATT_WARPS * ATT_GB) * sizeof(float);
     static size_t configured = 0;
@@ -242,7 +256,7 @@ static int launch_ck(const void* q, int q_stride, void* out, int out_stride, con
     rf_launch(attention_generic_kernel<T, CK>, grid, dim3(ATT_THREADS), smem, st,
         reinterpret_cast<const T*>(q), q_stride, reinterpret_cast<T*>(out), out_stride,
         reinterpret_cast<const T*>(k_pages), reinterpret_cast<const T*>(v_pages), tok_seq, tok_pos, seq_slot,
-        block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, hpb, keep_first);
+        block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, hpb, keep_first, sinks);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -251,15 +265,16 @@ template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                   const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                   const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
-                  const float* slopes, int window, int T_, cudaStream_t st, int keep_first = 0) {
+                  const float* slopes, int window, int T_, cudaStream_t st, int keep_first = 0,
+                  const float* sinks = nullptr) {
     if (T_ <= 0) return 0;
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (hd <= 0 || hd > ATT_MAX_HD || hdv <= 0 || hdv > ATT_MAX_HD || nkv <= 0 || nh % nkv || nkv > 65535) return RF_ERR_UNSUPPORTED;
     if (hd <= 256 && hdv <= 256)
         return launch_ck<T, 128>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                                 max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
+                                 max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first, sinks);
     return launch_ck<T, 64>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                            max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
+                            max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first, sinks);
 }
 
 extern "C" int rf_attention_generic(int dtype, const void* q, int q_stride, void* out, int out_stride,
@@ -288,4 +303,19 @@ extern "C" int rf_attention_generic_ext(int dtype, const void* q, int q_stride, 
                         max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first)
         : launch<__nv_bfloat16>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
                                 block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first);
+}
+
+// The same with a sink per head (float32 [nh], null: none): exp(sink) counts once in the softmax's denominator, with no
+// key, no value and no scaling.
+extern "C" int rf_attention_generic_sink(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                                         const void* k_pages, const void* v_pages, const int* tok_seq,
+                                         const int* tok_pos, const int* seq_slot, const int* block_table,
+                                         int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
+                                         const float* slopes, int window, int keep_first, const float* sinks, int T_,
+                                         cudaStream_t st) {
+    return dtype == 0
+        ? launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
+                        max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first, sinks)
+        : launch<__nv_bfloat16>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
+                                max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st, keep_first, sinks);
 }

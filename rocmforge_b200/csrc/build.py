@@ -37,6 +37,7 @@ MODULES: Dict[str, List[str]] = {
     "moe": ["moe.cu", "common.cuh"],
     "mamba2": ["mamba2.cu", "common.cuh"],
     "mlstm": ["mlstm.cu", "common.cuh"],
+    "delta": ["delta.cu", "common.cuh"],
     "random_fill": ["random_fill.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05_common.cuh", "common.cuh"],
     # has one CTA load a tile for its whole cluster (this GPU's memory only): a file of its own, left out of

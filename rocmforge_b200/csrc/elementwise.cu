@@ -40,7 +40,7 @@ template <> struct Four<__nv_bfloat16> {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int H, int V, const T* __restrict__ pos_table,
-                             const int* __restrict__ tok_pos, int P, T* __restrict__ rounded) {
+                             const int* __restrict__ tok_pos, int P, T* __restrict__ rounded, float scale) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -53,7 +53,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         ps = ps < 0 ? 0 : (ps >= P ? P - 1 : ps);       // the cache refuses sequences longer than the table
         const T* prow = pos_table != nullptr ? pos_table + (size_t)ps * H : nullptr;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = Cvt<T>::to_f32(row[i]) + (prow != nullptr ? Cvt<T>::to_f32(prow[i]) : 0.f);
+            const float v = Cvt<T>::to_f32(row[i]) * scale + (prow != nullptr ? Cvt<T>::to_f32(prow[i]) : 0.f);
             o[i] = v;
             if (rounded != nullptr) rounded[(size_t)t * H + i] = Cvt<T>::from_f32(v);
         }
@@ -65,11 +65,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
             float v[4];
             Four<T>::load(row + i, v);
-            *reinterpret_cast<float4*>(o + i) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(o + i) = make_float4(v[0] * scale, v[1] * scale, v[2] * scale, v[3] * scale);
         }
         return;
     }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Cvt<T>::to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Cvt<T>::to_f32(row[i]) * scale;
 }
 
 // ---------------------------------------------------------------- add + RMSNorm
@@ -570,6 +570,18 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int 
 // all query heads and one for all key heads), multiplied by it; then the first rot_dim elements turn as in the kernel
 // above (rot_dim 0: none); q goes to q_out, k and v into the page of (slot, position).  Key pages are
 // [n_pages, nkv, RF_PAGE, hd], value pages [n_pages, nkv, RF_PAGE, hdv].
+// What the per-head writer does beyond norm and rotation (all off when zero): a bias on the q | k | v columns, the norm
+// taken after the rotation instead of before it, a temperature on the queries, 1 + q_coef ln(floor((pos + 1) / q_every) + 1),
+// and rows without value columns whose keys are also their values (q | k; the caller reads values from the key pages).
+struct HeadWriteExtras {
+    const void* bias;
+    int bias_is_f32;
+    int norm_after;
+    float q_coef;
+    int q_every;
+    int v_is_k;
+};
+
 template <typename T, bool PARTIALS>
 __global__ void __launch_bounds__(128)
 head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_partials, size_t partial_stride,
@@ -579,18 +591,21 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
                           const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
                           T* __restrict__ v_pages, int write_kv, int rot_dim, int interleaved, int unit_norm, float eps,
                           const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_is_f32,
-                          float magnitude) {
-    extern __shared__ float heads_buf[];            // [warps][max(hd, hdv)]
+                          float magnitude, HeadWriteExtras ex) {
+    extern __shared__ float heads_buf[];            // [warps][2][max(hd, hdv)]
     pdl_trigger();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int hmax = hd > hdv ? hd : hdv;
-    float* buf = heads_buf + warp * hmax;
+    float* buf = heads_buf + warp * 2 * hmax;
+    float* turned = buf + hmax;
     const int pos = tok_pos[t];
     const int slot = seq_slot[tok_seq[t]];
     const int page = write_kv ? block_table[(size_t)slot * max_pages + pos / RF_PAGE] : 0;
     const int rh = rot_dim >> 1;
+    // a query's temperature grows with its position in steps of q_every positions
+    const float q_temp = ex.q_every > 0 ? 1.f + ex.q_coef * logf((float)((pos + 1) / ex.q_every) + 1.f) : 1.f;
     pdl_wait();
-    const int n_heads_all = write_kv ? nh + 2 * nkv : nh;
+    const int n_heads_all = write_kv ? nh + (ex.v_is_k ? 1 : 2) * nkv : nh;
     for (int head = blockIdx.y * nwarp + warp; head < n_heads_all; head += gridDim.y * nwarp) {
         const bool is_v = head >= nh + nkv;
         const int n = is_v ? hdv : hd;
@@ -606,20 +621,24 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
             } else {
                 x = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col + e]);
             }
+            if (ex.bias != nullptr) x += load_vec(ex.bias, ex.bias_is_f32, col + e);
             buf[e] = x;
             ss += x * x;
         }
+        const bool normed = unit_norm && !is_v;
         float r = 1.f;
-        if (unit_norm && !is_v) r = rsqrtf(warp_sum(ss) / (float)n + eps);
-        const void* nw = (unit_norm && !is_v) ? (head < nh ? q_norm_w : k_norm_w) : nullptr;
+        if (normed && !ex.norm_after) r = rsqrtf(warp_sum(ss) / (float)n + eps);
+        const void* nw = normed ? (head < nh ? q_norm_w : k_norm_w) : nullptr;
         __syncwarp();
-        if (nw != nullptr) {                              // the weighted norm comes before the rotation
+        if (nw != nullptr && !ex.norm_after) {            // the weighted norm comes before the rotation
             for (int e = lane; e < n; e += 32) buf[e] *= load_vec(nw, norm_w_is_f32, e);
             __syncwarp();
         }
         T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
                : !is_v ? k_pages + ((size_t)page * nkv + (head - nh)) * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd
                        : v_pages + ((size_t)page * nkv + (head - nh - nkv)) * RF_PAGE * hdv + (size_t)(pos % RF_PAGE) * hdv;
+        const float out_scale = head < nh ? q_temp : 1.f;
+        float ss2 = 0.f;
         for (int e = lane; e < n; e += 32) {
             float x = buf[e] * r;
             if (!is_v && e < rot_dim) {
@@ -632,7 +651,16 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
                 const float y = buf[partner] * r;
                 x = first ? x * c - y * s : x * c + y * s;
             }
-            dst[e] = Cvt<T>::from_f32(x);
+            if (normed && ex.norm_after) { turned[e] = x; ss2 += x * x; }
+            else dst[e] = Cvt<T>::from_f32(x * out_scale);
+        }
+        if (normed && ex.norm_after) {                    // the head is divided by its root mean square as it is after the rotation
+            const float r2 = rsqrtf(warp_sum(ss2) / (float)n + eps);
+            for (int e = lane; e < n; e += 32) {          // (a lane reads what it wrote)
+                float x = turned[e] * r2;
+                if (nw != nullptr) x *= load_vec(nw, norm_w_is_f32, e);
+                dst[e] = Cvt<T>::from_f32(x * out_scale);
+            }
         }
         __syncwarp();
     }
@@ -769,6 +797,85 @@ scaled_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int n0, c
     }
 }
 
+// ---------------------------------------------------------------- h += s0 * a0 + s1 * a1, then the next RMS norm
+// Two sub-layer results side by side, each float32 [rows][H] or a stack of n partial sums added in index order, each
+// with a factor of its own; the sum goes into the 32-bit stream.  With w_next the norm that reads the stream next is
+// computed in the same pass: y = h / sqrt(mean(h^2) + eps) * w_next, in the compute dtype.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+weighted_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int n0, float s0, const float* __restrict__ a1, int n1,
+                    float s1, size_t part_stride, const void* __restrict__ w_next, int w_is_f32, float eps,
+                    T* __restrict__ y_next, int H) {
+    extern __shared__ float row[];                  // [H], 34 for the sums
+    float* red = row + H;
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * H;
+    pdl_wait();
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float x = 0.f, z = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
+        if (a1 != nullptr) {
+#pragma unroll 4
+            for (int s = 0; s < n1; ++s) z += a1[(size_t)s * part_stride + base + c];
+        }
+        const float v = h[base + c] + (s0 * x + s1 * z);
+        h[base + c] = v;
+        row[c] = v;
+        ss += v * v;
+    }
+    if (y_next == nullptr) return;
+    const float r = rsqrtf(block_sum(ss, red) / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x)        // a thread reads what it wrote
+        y_next[base + c] = Cvt<T>::from_f32(row[c] * r * load_vec(w_next, w_is_f32, c));
+}
+
+template <typename T>
+static int launch_weighted_add(float* h, const float* a0, int n0, float s0, const float* a1, int n1, float s1,
+                               const void* w_next, int w_is_f32, float eps, void* y_next, int rows, int H, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (a0 == nullptr || n0 < 1 || (a1 != nullptr && n1 < 1) || (y_next != nullptr && w_next == nullptr)) return RF_ERR_BAD_ARG;
+    const size_t smem = ((size_t)H + 34) * sizeof(float);
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(weighted_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    int threads = 256;
+    if (rows <= 296) { threads = (H + 31) / 32 * 32; if (threads > 1024) threads = 1024; if (threads < 256) threads = 256; }
+    rf_launch(weighted_add_kernel<T>, dim3(rows), dim3(threads), smem, st, h, a0, n0, s0, a1, n1, s1, (size_t)rows * H, w_next,
+              w_is_f32, eps, reinterpret_cast<T*>(y_next), H);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- RMS norms of stretches of a row
+// Block (t, j) norms columns col[j] .. col[j] + n[j] of row t of src: y = x / sqrt(mean(x^2) + eps) * w_j (w_j null: no
+// weight), sums in 32-bit, and writes them to out_j [T][n_j] (row stride given).  Up to two stretches a launch.
+struct NormStretch {
+    int col, n;
+    const void* w;
+    void* out;
+    int out_stride;
+};
+template <typename T>
+__global__ void __launch_bounds__(256)
+stretch_norm_kernel(const T* __restrict__ src, int src_stride, NormStretch a, NormStretch b, int w_is_f32, float eps) {
+    __shared__ float red[34];
+    pdl_trigger();
+    const NormStretch s = blockIdx.y == 0 ? a : b;
+    const T* x = src + (size_t)blockIdx.x * src_stride + s.col;
+    T* y = reinterpret_cast<T*>(s.out) + (size_t)blockIdx.x * s.out_stride;
+    pdl_wait();
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < s.n; c += blockDim.x) { const float v = Cvt<T>::to_f32(x[c]); ss += v * v; }
+    const float r = rsqrtf(block_sum(ss, red) / (float)s.n + eps);
+    for (int c = threadIdx.x; c < s.n; c += blockDim.x)
+        y[c] = Cvt<T>::from_f32(Cvt<T>::to_f32(x[c]) * r * (s.w != nullptr ? load_vec(s.w, w_is_f32, c) : 1.f));
+}
+
 // ---------------------------------------------------------------- x <- cap * tanh(x / cap), in place (logits)
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
     pdl_trigger();
@@ -864,11 +971,12 @@ static int launch_round_rows(const float* h, void* out, long long n, cudaStream_
 
 template <typename T>
 static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st,
-                        const void* pos_table = nullptr, const int* tok_pos = nullptr, int P = 0, void* rounded = nullptr) {
+                        const void* pos_table = nullptr, const int* tok_pos = nullptr, int P = 0, void* rounded = nullptr,
+                        float scale = 1.f) {
     if (T_ <= 0) return 0;
     if (pos_table != nullptr && (tok_pos == nullptr || P <= 0)) return RF_ERR_BAD_ARG;
     rf_launch(embed_kernel<T>, dim3(T_), dim3(256), 0, st, reinterpret_cast<const T*>(table), ids, out, H, V,
-              reinterpret_cast<const T*>(pos_table), tok_pos, P, reinterpret_cast<T*>(rounded));
+              reinterpret_cast<const T*>(pos_table), tok_pos, P, reinterpret_cast<T*>(rounded), scale);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -1027,25 +1135,25 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
                                      int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, int rot_dim,
                                      int interleaved, int unit_norm, float eps, cudaStream_t st,
                                      const void* q_norm_w = nullptr, const void* k_norm_w = nullptr, int norm_w_is_f32 = 0,
-                                     float magnitude = 1.f) {
+                                     float magnitude = 1.f, HeadWriteExtras ex = HeadWriteExtras{nullptr, 0, 0, 0.f, 0, 0}) {
     if (T_ <= 0) return 0;
-    if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0) return RF_ERR_BAD_ARG;
-    const size_t smem = (size_t)4 * (hd > hdv ? hd : hdv) * sizeof(float);
+    if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0 || ex.q_every < 0) return RF_ERR_BAD_ARG;
+    const size_t smem = (size_t)4 * 2 * (hd > hdv ? hd : hdv) * sizeof(float);
     if (smem > 48 * 1024) return RF_ERR_UNSUPPORTED;
     // few tokens: a token's heads over several blocks (a warp per head)
-    const int all_heads = write_kv ? nh + 2 * nkv : nh;
+    const int all_heads = write_kv ? nh + (ex.v_is_k ? 1 : 2) * nkv : nh;
     int by = T_ >= 512 ? 1 : (all_heads + 3) / 4;
     if (by > 64) by = 64;
     if (n_partials > 0)
         rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_, by), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
-                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
+                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude, ex);
     else
         rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_, by), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
-                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
+                  q_norm_w, k_norm_w, norm_w_is_f32, magnitude, ex);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -1055,6 +1163,11 @@ extern "C" {
 int rf_embed(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
     return dtype == 0 ? launch_embed<float>(table, ids, out, T_, H, V, st)
                       : launch_embed<__nv_bfloat16>(table, ids, out, T_, H, V, st);
+}
+// out[t] = table[ids[t]] * scale, the product formed in 32-bit.
+int rf_embed_scaled(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, float scale, cudaStream_t st) {
+    return dtype == 0 ? launch_embed<float>(table, ids, out, T_, H, V, st, nullptr, nullptr, 0, nullptr, scale)
+                      : launch_embed<__nv_bfloat16>(table, ids, out, T_, H, V, st, nullptr, nullptr, 0, nullptr, scale);
 }
 // The same with a learned position table [P, H] (row tok_pos[t] is added; null: none) and a copy of the result in the
 // table's dtype (rounded; null: none).
@@ -1133,6 +1246,27 @@ int rf_head_norm_kv_write_w(int dtype, const void* src, int row_stride, int n_pa
                                                    max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
                                                    unit_norm, eps, st, q_norm_w, k_norm_w, norm_w_is_f32, magnitude);
 }
+// The same with a bias on the columns read ([q | k | v], null: none), the norm taken after the rotation (norm_after), a
+// temperature on the queries (q_every > 0: 1 + q_coef ln(floor((pos + 1) / q_every) + 1)) and rows q | k whose keys are
+// their values (v_is_k: nothing is written to value pages).
+int rf_head_norm_kv_write_x(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride, void* q_out,
+                            int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq, const int* tok_seq,
+                            const int* tok_pos, const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
+                            void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, int unit_norm, float eps,
+                            const void* q_norm_w, const void* k_norm_w, int norm_w_is_f32, float magnitude,
+                            const void* bias, int bias_is_f32, int norm_after, float q_coef, int q_every, int v_is_k,
+                            cudaStream_t st) {
+    const HeadWriteExtras ex{bias, bias_is_f32, norm_after, q_coef, q_every, v_is_k};
+    return dtype == 0
+        ? launch_head_norm_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride, nh, nkv,
+                                           hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, max_pages, k_pages,
+                                           v_pages, write_kv, T_, rot_dim, interleaved, unit_norm, eps, st, q_norm_w, k_norm_w,
+                                           norm_w_is_f32, magnitude, ex)
+        : launch_head_norm_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride,
+                                                   nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                                                   max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
+                                                   unit_norm, eps, st, q_norm_w, k_norm_w, norm_w_is_f32, magnitude, ex);
+}
 int rf_clamped_glu(int dtype, const void* gu, void* a, int T_, int I, float limit, float alpha, const float* row_scale,
                    cudaStream_t st) {
     return dtype == 0 ? launch_clamped_glu<float>(gu, a, T_, I, limit, alpha, row_scale, st)
@@ -1160,6 +1294,26 @@ int rf_scaled_add(int dtype, float* h, const float* a0, int n0, const void* w0, 
     return dtype == 0
         ? launch_scaled_add<float>(h, a0, n0, w0, a1, n1, w1, w_is_f32, eps, mult, alpha, w_next, b_next, y_next, rows, H, st)
         : launch_scaled_add<__nv_bfloat16>(h, a0, n0, w0, a1, n1, w1, w_is_f32, eps, mult, alpha, w_next, b_next, y_next, rows, H, st);
+}
+// h [rows][H] += s0 * sum(a0 parts) + s1 * sum(a1 parts) (a1 null: one addend); with y_next (of dtype) also the RMS norm of
+// the new rows with w_next and eps.
+int rf_weighted_add(int dtype, float* h, const float* a0, int n0, float s0, const float* a1, int n1, float s1,
+                    const void* w_next, int w_is_f32, float eps, void* y_next, int rows, int H, cudaStream_t st) {
+    return dtype == 0 ? launch_weighted_add<float>(h, a0, n0, s0, a1, n1, s1, w_next, w_is_f32, eps, y_next, rows, H, st)
+                      : launch_weighted_add<__nv_bfloat16>(h, a0, n0, s0, a1, n1, s1, w_next, w_is_f32, eps, y_next, rows, H, st);
+}
+// RMS norms of one or two stretches of the rows of src [T][src_stride] (n1 0: one stretch); see stretch_norm_kernel.
+int rf_stretch_norm(int dtype, const void* src, int src_stride, int col0, int n0, const void* w0, void* out0, int out0_stride,
+                    int col1, int n1, const void* w1, void* out1, int out1_stride, int w_is_f32, float eps, int T_,
+                    cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (n0 <= 0 || n1 < 0) return RF_ERR_BAD_ARG;
+    const NormStretch a{col0, n0, w0, out0, out0_stride}, b{col1, n1, w1, out1, out1_stride};
+    const dim3 grid(T_, n1 > 0 ? 2 : 1);
+    if (dtype == 0) rf_launch(stretch_norm_kernel<float>, grid, dim3(256), 0, st, reinterpret_cast<const float*>(src), src_stride, a, b, w_is_f32, eps);
+    else rf_launch(stretch_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(src), src_stride, a, b, w_is_f32, eps);
+    RF_LAUNCH_CHECK();
+    return 0;
 }
 int rf_softcap(float* x, long long n, float cap, cudaStream_t st) {
     if (n <= 0) return 0;

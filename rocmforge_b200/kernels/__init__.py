@@ -8,5 +8,6 @@ from .basic import (relu2, add_row, branch_norm_add, head_norm_kv_write, gemm_si
                     retention_scan, retention_gate, retention_chunked, RETENTION_CHUNK, moe_route, moe_sort, moe_combine, moe_gather, MOE_TILE_SMALL, MOE_TILE_LARGE, MOE_TILE_TC)
 from .basic import (embed_positions, round_rows, clamped_glu, sigmoid_gate, key_span, gla_prepare, gla_scan, MOE_SCORINGS)
 from .basic import (dyt_rows, scaled_add, softcap_, gated_scan, gated_chunked, mlstm_prepare, mlstm_gates, conv_silu, mamba_gates, mamba_finish)
+from .basic import (weighted_add, stretch_norm, delta_prepare, delta_scan)
 from ._ffi import launch_count
 from . import tensor_core

@@ -20,8 +20,8 @@ def _f(module, name, *argtypes):
     return fn(module, name, list(argtypes))
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] widened to float32."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] widened to float32 (times ``scale``, the product formed in 32-bit)."""
     need_cuda(table, ids)
     need(table.dim() == 2 and table.is_contiguous(), "embed: table must be a contiguous matrix")
     need(ids.dtype == torch.int32 and ids.dim() == 1, "embed: ids must be a 1-d int32 tensor")
@@ -29,6 +29,10 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = Non
     T = ids.shape[0]
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    if scale is not None and float(scale) != 1.0:
+        f = _f("elementwise", "rf_embed_scaled", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p)
+        check(f(dtype_code(table.dtype), ptr(table), ptr(ids), ptr(out), T, H, V, float(scale), stream()), "embed")
+        return out
     f = _f("elementwise", "rf_embed", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(table.dtype), ptr(table), ptr(ids), ptr(out), T, H, V, stream()), "embed")
     return out
@@ -268,10 +272,12 @@ def key_span(window: int | None, chunk: int | None = None) -> int:
 def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                       tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                       out: torch.Tensor | None = None, *, v_head_dim: int | None = None, softcap: float | None = None,
-                      slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                      slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
+                      sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of the T new tokens over the paged cache (their own keys included).  ``window`` / ``chunk``: see
     ``key_span``.  ``keep_first``: with a window, the first ``keep_first`` positions of a sequence stay visible to every
-    later query as well (at their own positions).
+    later query as well (at their own positions).  ``sinks`` (float32 [heads]): exp(sinks[head]) is one more term of the
+    softmax's denominator; it has no key and no value and is not scaled.
 
     ``v_head_dim``: size of a value head where it differs from a key head's (the output is [T, heads * v_head_dim]);
     ``softcap``: scores become softcap * tanh(score / softcap); ``slopes`` (float32 [heads]): after the cap, a score is
@@ -288,6 +294,20 @@ def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
         out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
     window = key_span(window, chunk)
     keep_first = int(keep_first or 0) if window > 0 else 0         # without a window every key is visible anyway
+    if sinks is not None:
+        need_cuda(sinks)
+        need(sinks.dtype == torch.float32 and sinks.shape == (n_heads,) and sinks.is_contiguous()
+             and (slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous())),
+             "attention: sinks (and slopes) must be float32 [heads]")
+        f = _f("attention_generic", "rf_attention_generic_sink", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+               c_void_p, c_int, c_int, c_void_p, c_int, c_void_p)
+        check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
+                ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
+                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), window, keep_first, ptr(sinks), T,
+                stream()),
+              f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, v_head_dim={vd}, sinks)")
+        return out
     if vd != head_dim or softcap or slopes is not None or keep_first:
         need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
              "attention: slopes must be float32 [heads]")
@@ -639,8 +659,15 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
                        compute_dtype: torch.dtype | None = None, rot_dim: int = 0, interleaved: bool = False,
                        unit_norm_eps: float | None = None, q_norm_weight: torch.Tensor | None = None,
-                       k_norm_weight: torch.Tensor | None = None, magnitude: float = 1.0) -> torch.Tensor:
+                       k_norm_weight: torch.Tensor | None = None, magnitude: float = 1.0, bias: torch.Tensor | None = None,
+                       norm_after_rotation: bool = False, q_temperature=None, values_are_keys: bool = False) -> torch.Tensor:
     """q | k | v rows on their way into the cache, for heads that are normed and for values of another size than keys.
+
+    More options: ``bias`` ([width] in float32 or bfloat16) is added to the columns read; ``norm_after_rotation``: the
+    heads are divided by their root mean square as they are after the rotation (and then weighted), not before it;
+    ``q_temperature`` = (coef, every): a query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1);
+    ``values_are_keys``: the rows are q | k only, the keys are written and ``v_pages`` is not touched (the caller reads
+    values from the key pages; ``v_head_dim`` must equal ``head_dim``).
 
     ``qkv`` is [T, heads*head_dim + kv_heads*head_dim + kv_heads*v_head_dim] in the compute dtype, or a float32 stack
     [S, T, ...] of partial sums.  With ``unit_norm_eps`` every query and key head is divided by its root mean square
@@ -650,7 +677,8 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     Returns q [T, heads*head_dim] in the compute dtype; k and v go to their pages.
     """
     need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages)
-    width = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
+    need(not values_are_keys or v_head_dim == head_dim, "head_norm_kv_write: keys that are values have the keys' size")
+    width = (n_heads + n_kv_heads) * head_dim + (0 if values_are_keys else n_kv_heads * v_head_dim)
     partials = qkv.dim() == 3
     if partials:
         need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] >= (width if write_kv else n_heads * head_dim) and compute_dtype is not None,
@@ -664,8 +692,8 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
          "head_norm_kv_write: inv_freq must hold rot_dim/2 float32 frequencies")
     if write_kv:
         need(k_pages is not None and k_pages.dtype == dt and k_pages.is_contiguous()
-             and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and v_pages is not None and v_pages.dtype == dt
-             and v_pages.is_contiguous() and tuple(v_pages.shape[1:]) == (n_kv_heads, PAGE, v_head_dim),
+             and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and (values_are_keys or (v_pages is not None and v_pages.dtype == dt
+             and v_pages.is_contiguous() and tuple(v_pages.shape[1:]) == (n_kv_heads, PAGE, v_head_dim))),
              "head_norm_kv_write: pages must be [n_pages, kv_heads, 64, head size] of the compute dtype")
     q_out = torch.empty((T, n_heads * head_dim), dtype=dt, device=qkv.device)
     nws = [w for w in (q_norm_weight, k_norm_weight) if w is not None]
@@ -673,6 +701,23 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     need(all(w.shape == (head_dim,) and w.is_contiguous() and w.dtype == nws[0].dtype for w in nws)
          and (not nws or (unit_norm_eps is not None and nws[0].dtype in (torch.float32, torch.bfloat16))),
          "head_norm_kv_write: norm weights are [head_dim] vectors of one dtype and go with unit_norm_eps")
+    if bias is not None or norm_after_rotation or q_temperature is not None or values_are_keys:
+        need_cuda(bias)
+        need(bias is None or (bias.shape == (width,) and bias.is_contiguous() and bias.dtype in (torch.float32, torch.bfloat16)),
+             "head_norm_kv_write: the bias must be [width] in float32 or bfloat16")
+        coef, every = (float(q_temperature[0]), int(q_temperature[1])) if q_temperature is not None else (0.0, 0)
+        need(q_temperature is None or every >= 1, "head_norm_kv_write: the temperature's step must be at least one position")
+        f = _f("elementwise", "rf_head_norm_kv_write_x", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
+               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+               c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p)
+        check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(q_out), q_out.stride(0), n_heads, n_kv_heads, head_dim,
+                v_head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
+                ptr(k_pages), ptr(None if values_are_keys else v_pages), int(write_kv), T, int(rot_dim), int(interleaved),
+                int(unit_norm_eps is not None), float(unit_norm_eps or 0.0), ptr(q_norm_weight), ptr(k_norm_weight),
+                int(bool(nws) and nws[0].dtype == torch.float32), float(magnitude), ptr(bias),
+                int(bias is not None and bias.dtype == torch.float32), int(bool(norm_after_rotation)), coef, every,
+                int(bool(values_are_keys)), stream()), "head_norm_kv_write")
+        return q_out
     f = _f("elementwise", "rf_head_norm_kv_write_w", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
            c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p)
@@ -1157,3 +1202,113 @@ def mamba_finish(y: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, skip: tor
     check(f(dtype_code(gate.dtype), ptr(y), ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(skip), ptr(norm_w),
             int(skip.dtype == torch.float32), ptr(out), T, inner, parts, vdim, float(eps), stream()), "mamba_finish")
     return out
+
+
+# ---------------------------------------------------------------- two results side by side, each with a factor
+
+def weighted_add(h: torch.Tensor, addends, compute_dtype: torch.dtype, *, next_norm=None) -> torch.Tensor | None:
+    """h += s0 a0 (+ s1 a1) for ``addends`` = [(a0, s0)] or [(a0, s0), (a1, s1)], in 32-bit and one pass over the rows; an
+    addend is float32 [T, H] or a stack [S, T, H] of a K-split product's partial sums, added here in index order.  With
+    ``next_norm`` = (weight [H], eps) returns rms(h) * weight of the new rows in the compute dtype, else None."""
+    need(len(addends) in (1, 2), "weighted_add: one or two addends")
+    (a0, s0), (a1, s1) = addends[0], (addends[1] if len(addends) == 2 else (None, 0.0))
+    w, eps = next_norm if next_norm is not None else (None, 0.0)
+    need_cuda(h, a0, a1, w)
+    T, H = h.shape
+    need(h.dtype == torch.float32 and h.is_contiguous(), "weighted_add: h must be contiguous float32 [T, H]")
+    for a in (a0, a1):
+        need(a is None or (a.dtype == torch.float32 and tuple(a.shape[-2:]) == (T, H) and a.dim() in (2, 3) and a.is_contiguous()),
+             "weighted_add: an addend must be contiguous float32 [T, H] or [S, T, H]")
+    need(w is None or (w.shape == (H,) and w.is_contiguous() and w.dtype in (torch.float32, torch.bfloat16)),
+         "weighted_add: the next norm's weight must be [H] in float32 or bfloat16")
+    n0 = a0.shape[0] if a0.dim() == 3 else 1
+    n1 = (a1.shape[0] if a1.dim() == 3 else 1) if a1 is not None else 0
+    y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if w is not None else None
+    f = _f("elementwise", "rf_weighted_add", c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_float, c_void_p, c_int,
+           c_float, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), n0, float(s0), ptr(a1), n1, float(s1), ptr(w),
+            int(w is not None and w.dtype == torch.float32), float(eps), ptr(y), T, H, stream()), f"weighted_add (H={H})")
+    return y
+
+
+def stretch_norm(src: torch.Tensor, stretches, eps: float):
+    """RMS norms of stretches of the rows of ``src`` [T, columns]: for every (col, n, weight) of ``stretches`` (one or two;
+    weight [n] or None) a tensor [T, n] of src's dtype, x / sqrt(mean(x^2) + eps) * weight over columns col .. col + n,
+    sums in 32-bit; one launch."""
+    need(len(stretches) in (1, 2), "stretch_norm: one or two stretches")
+    ws = [w for _, _, w in stretches if w is not None]
+    need_cuda(src, *ws)
+    need(src.dim() == 2 and src.stride(1) == 1, "stretch_norm: src must be [T, columns] with unit inner stride")
+    need(all(0 <= c and n >= 1 and c + n <= src.shape[1] for c, n, _ in stretches), "stretch_norm: a stretch leaves the row")
+    need(all(w.shape == (n,) and w.is_contiguous() for _, n, w in stretches if w is not None)
+         and all(w.dtype == ws[0].dtype for w in ws) and (not ws or ws[0].dtype in (torch.float32, torch.bfloat16)),
+         "stretch_norm: weights are [n] vectors of one dtype, float32 or bfloat16")
+    T = src.shape[0]
+    outs = [torch.empty((T, n), dtype=src.dtype, device=src.device) for _, n, _ in stretches]
+    (c0, n0, w0), o0 = stretches[0], outs[0]
+    (c1, n1, w1), o1 = (stretches[1], outs[1]) if len(stretches) == 2 else ((0, 0, None), None)
+    f = _f("elementwise", "rf_stretch_norm", c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+           c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
+    check(f(dtype_code(src.dtype), ptr(src), src.stride(0), int(c0), int(n0), ptr(w0), ptr(o0), n0, int(c1), int(n1), ptr(w1),
+            ptr(o1), n1, int(bool(ws) and ws[0].dtype == torch.float32), float(eps), T, stream()), "stretch_norm")
+    return outs
+
+
+# ---------------------------------------------------------------- gated delta rule (csrc/delta.cu)
+
+def delta_prepare(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, beta_src: torch.Tensor,
+                  heads: int, qk_heads: int, dim: int, q_scale: float, unit_eps: float):
+    """What the gated delta rule's recurrence reads, all float32: (qn, kn, kq, decay, beta).
+
+    ``qkv`` float32 [T, >= 2 qk_heads dim]: q heads, then k heads (the values that follow are left alone); qn = q / sqrt(sum
+    q^2 + unit_eps) * q_scale and kn likewise without the scale, per head, [T, qk_heads*dim]; kq [T, qk_heads] = kn . qn;
+    decay [T, heads*dim] = exp(-exp(a_log[head]) softplus(a + dt_bias)) with ``a`` float32 [T, heads*dim]; beta [T, heads] =
+    sigmoid(beta_src), ``beta_src`` a [T, heads] view of the projection's output."""
+    need_cuda(qkv, a, dt_bias, a_log, beta_src)
+    T = qkv.shape[0]
+    need(qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * qk_heads * dim,
+         "delta_prepare: qkv must be float32 [T, >= 2 qk_heads dim]")
+    need(a.dtype == torch.float32 and a.shape == (T, heads * dim) and a.is_contiguous(), "delta_prepare: a must be float32 [T, heads*dim]")
+    need(dt_bias.shape == (heads * dim,) and a_log.shape == (heads,) and dt_bias.dtype == a_log.dtype and dt_bias.is_contiguous()
+         and a_log.is_contiguous() and a_log.dtype in (torch.float32, torch.bfloat16),
+         "delta_prepare: dt_bias [heads*dim] and a_log [heads] of one dtype")
+    need(beta_src.shape == (T, heads) and beta_src.stride(1) == 1 and beta_src.dtype in (torch.float32, torch.bfloat16),
+         "delta_prepare: beta_src must be a [T, heads] view")
+    need(heads % qk_heads == 0, "delta_prepare: the q/k heads must divide the heads")
+    dev = qkv.device
+    qn = torch.empty((T, qk_heads * dim), dtype=torch.float32, device=dev)
+    kn = torch.empty_like(qn)
+    kq = torch.empty((T, qk_heads), dtype=torch.float32, device=dev)
+    decay = torch.empty((T, heads * dim), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    f = _f("delta", "rf_delta_prepare", c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p)
+    check(f(dtype_code(beta_src.dtype), ptr(qkv), qkv.stride(0), ptr(a), ptr(dt_bias), ptr(a_log), int(a_log.dtype == torch.float32),
+            ptr(beta_src), beta_src.stride(0), ptr(qn), ptr(kn), ptr(kq), ptr(decay), ptr(beta), heads, qk_heads, dim,
+            float(q_scale), float(unit_eps), T, stream()), "delta_prepare")
+    return qn, kn, kq, decay, beta
+
+
+def delta_scan(qn: torch.Tensor, kn: torch.Tensor, kq: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, v: torch.Tensor,
+               state: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor, heads: int, qk_heads: int, dim: int,
+               vdim: int) -> torch.Tensor:
+    """The gated delta rule, token by token for every sequence of the step, per head (head h reads q/k head h // (heads /
+    qk_heads)):  S <- diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t.
+
+    ``state`` float32 [slots, heads, dim, vdim] is read and replaced; ``v`` float32 [T, >= heads*vdim] view; returns o float32
+    [T, heads*vdim].  The sums' order depends on (dim, position) alone."""
+    need_cuda(qn, kn, kq, decay, beta, v, state, cu_q, seq_slot)
+    T = qn.shape[0]
+    B = seq_slot.shape[0]
+    need(all(x.dtype == torch.float32 and x.is_contiguous() for x in (qn, kn, kq, decay, beta, state)), "delta_scan: float32 inputs")
+    need(qn.shape == (T, qk_heads * dim) and kn.shape == qn.shape and kq.shape == (T, qk_heads) and decay.shape == (T, heads * dim)
+         and beta.shape == (T, heads), "delta_scan: shapes of qn, kn, kq, decay, beta")
+    need(v.dtype == torch.float32 and v.dim() == 2 and v.stride(1) == 1 and v.shape == (T, heads * vdim), "delta_scan: v must be float32 [T, heads*vdim]")
+    need(tuple(state.shape[1:]) == (heads, dim, vdim), "delta_scan: state must be [slots, heads, dim, vdim]")
+    need(dim <= 256, "delta_scan: at most 256 key channels a head")
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qn.device)
+    f = _f("delta", "rf_delta_scan", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(ptr(qn), ptr(kn), ptr(kq), ptr(decay), ptr(beta), ptr(v), v.stride(0), ptr(state), ptr(o), ptr(cu_q), ptr(seq_slot),
+            B, heads, qk_heads, dim, vdim, stream()), f"delta_scan (heads={heads}, dim={dim}, vdim={vdim})")
+    return o

@@ -22,3 +22,5 @@ from .block import ScaledPreNormBlock
 from .mlp import SummedFeedForward
 from .mlstm import MatrixMemory
 from .mamba2 import StateSpaceDuality
+from .latent import LatentAttention
+from .delta import GatedDeltaRule

@@ -43,7 +43,13 @@ class GQAAttention(Mixer):
     their own positions; the cache keeps their pages) and ``gate`` "sigmoid_head" (one gate per head, W_g of ``heads``
     rows: head h's output is multiplied by sigmoid(W_g x)_h).  A position encoding whose rotation carries a ``magnitude``
     (sine and cosine times a factor) goes through the per-head writer as well.  Normed heads and values of another size go into the
-    cache through the per-head writer; a cap, slopes and kept first positions are known to the generic attention and to the
+    cache through the per-head writer.  ``sink``: a learned number per head (tensor ``names["sink"]``, [heads]) whose
+    exponential counts once in the softmax's denominator, with no key, no value and no scaling.
+    ``qk_norm_after_rotation``: the division of ``qk_norm_eps`` is applied to the heads as they are after the rotation.
+    ``q_temperature`` = (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).
+    ``values_are_keys``: the mixer has no value projection; its values are its keys as they lie in the cache, which then
+    holds keys alone.  With any of these (as with normed heads) biases are added by the per-head writer.
+    A cap, slopes and kept first positions are known to the generic attention and to the
     tcgen05 prompt attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
     on the same kernels as one without them.
     """
@@ -55,7 +61,8 @@ class GQAAttention(Mixer):
                  scale: Optional[float] = None, v_head_dim: Optional[int] = None, qk_norm_eps: Optional[float] = None,
                  softcap: Optional[float] = None, distance_slopes=None, names: Optional[Dict[str, str]] = None,
                  qk_norm_weight: bool = False, chunk: Optional[int] = None, gate: Optional[str] = None,
-                 shares_kv: bool = False, cache_keeps: Optional[str] = None, keep_first: int = 0):
+                 shares_kv: bool = False, cache_keeps: Optional[str] = None, keep_first: int = 0, sink: bool = False,
+                 qk_norm_after_rotation: bool = False, q_temperature=None, values_are_keys: bool = False):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
@@ -70,7 +77,8 @@ class GQAAttention(Mixer):
             raise ValueError(f"{len(self.distance_slopes)} distance slopes for {n_heads} heads")
         self.slopes_dev = None
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                      "g": "g_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+                      "g": "g_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks",
+                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
         self.names.update(names or {})
         self.chunk = int(chunk) if chunk else None
         if self.chunk is not None and window:
@@ -85,24 +93,40 @@ class GQAAttention(Mixer):
         if cache_keeps not in (None, "all"):
             raise ValueError(f"gqa_attention: cache_keeps {cache_keeps!r} (all, or None)")
         self.gate, self.shares_kv, self.cache_keeps = gate, bool(shares_kv), cache_keeps
+        self.sink = bool(sink)
+        self.sinks_dev = None
+        self.norm_after = bool(qk_norm_after_rotation)
+        if self.norm_after and qk_norm_eps is None:
+            raise ValueError("gqa_attention: qk_norm_after_rotation goes with qk_norm_eps")
+        self.q_temperature = None if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+        if self.q_temperature is not None and self.q_temperature[1] < 1:
+            raise ValueError("gqa_attention: the query temperature's step must be at least one position")
+        self.values_are_keys = bool(values_are_keys)
+        if self.values_are_keys and ((v_head_dim is not None and v_head_dim != head_dim) or shares_kv):
+            raise ValueError("gqa_attention: keys that serve as values have the keys' size and a cache of their own")
         self.qk_norm_weight = bool(qk_norm_weight)
         if self.qk_norm_weight and qk_norm_eps is None:
             raise ValueError("gqa_attention: norm weights go with qk_norm_eps")
         self.q_norm_w = self.k_norm_w = None
         self.q_size = n_heads * head_dim
         self.kv_size = n_kv_heads * head_dim
-        self.v_size = n_kv_heads * self.v_head_dim
+        self.v_size = 0 if self.values_are_keys else n_kv_heads * self.v_head_dim
         self.o_in = n_heads * self.v_head_dim
         self.gate_rows = n_heads if gate == "sigmoid_head" else self.o_in
         self.magnitude = float(((position.rotation() if position is not None else None) or {}).get("magnitude", 1.0))
         # normed heads and values of another size: the per-head cache writer; a cap or slopes: no mma.sync kernel knows them
         self.plain_projection = (self.v_head_dim != head_dim or self.qk_norm_eps is not None or self.gate is not None
-                                 or self.shares_kv or self.magnitude != 1.0)
+                                 or self.shares_kv or self.magnitude != 1.0 or self.q_temperature is not None
+                                 or self.values_are_keys)
         self.shaped_scores = self.softcap is not None or self.distance_slopes is not None
         self.plain_only = self.plain_projection or self.shaped_scores
-        if self.plain_only and (qkv_bias or o_bias):
-            raise ValueError("gqa_attention: biases do not go with normed heads, a score cap, distance slopes, another "
-                             "value size, a gate or a borrowed cache")
+        if self.plain_only and o_bias:
+            raise ValueError("gqa_attention: an output bias does not go with the per-head writer or shaped scores")
+        if self.shaped_scores and qkv_bias and not self.plain_projection:
+            raise ValueError("gqa_attention: biases with a score cap or distance slopes need the per-head writer")
+        if qkv_bias and self.shares_kv:
+            raise ValueError("gqa_attention: biases do not go with a borrowed cache")
+        self.plain_bias = None
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
 
@@ -111,7 +135,10 @@ class GQAAttention(Mixer):
         s = {n["q"]: ParamSpec((self.q_size, self.hidden)), n["o"]: ParamSpec((self.hidden, self.o_in))}
         if not self.shares_kv:
             s[n["k"]] = ParamSpec((self.kv_size, self.hidden))
-            s[n["v"]] = ParamSpec((self.v_size, self.hidden))
+            if not self.values_are_keys:
+                s[n["v"]] = ParamSpec((self.v_size, self.hidden))
+        if self.sink:
+            s[n["sink"]] = ParamSpec((self.n_heads,), kind="vector", init="normal", std=1.0)
         if self.gate is not None:
             s[n["g"]] = ParamSpec((self.gate_rows, self.hidden))
         if self.qk_norm_weight:
@@ -119,9 +146,10 @@ class GQAAttention(Mixer):
             if not self.shares_kv:
                 s[n["k_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="ones")
         if self.qkv_bias:
-            s["q_proj.bias"] = ParamSpec((self.q_size,), kind="vector")
-            s["k_proj.bias"] = ParamSpec((self.kv_size,), kind="vector")
-            s["v_proj.bias"] = ParamSpec((self.kv_size,), kind="vector")
+            s[n["q_bias"]] = ParamSpec((self.q_size,), kind="vector")
+            s[n["k_bias"]] = ParamSpec((self.kv_size,), kind="vector")
+            if not self.values_are_keys:
+                s[n["v_bias"]] = ParamSpec((self.v_size,), kind="vector")
         if self.o_bias:
             s["o_proj.bias"] = ParamSpec((self.hidden,), kind="vector")
         return s
@@ -129,7 +157,7 @@ class GQAAttention(Mixer):
     def bind(self, params, compute_dtype):
         n = self.names
         # one product for everything that reads the mixer's input: q | k | v | gate (k, v absent with a borrowed cache)
-        blocks = [params[n["q"]]] + ([] if self.shares_kv else [params[n["k"]], params[n["v"]]])
+        blocks = [params[n["q"]]] + ([] if self.shares_kv else [params[n["k"]]] + ([] if self.values_are_keys else [params[n["v"]]]))
         self.gate_col = self.q_size + (0 if self.shares_kv else self.kv_size + self.v_size)
         if self.gate is not None:
             g = params[n["g"]]
@@ -146,9 +174,13 @@ class GQAAttention(Mixer):
             self.k_norm_w = None if self.shares_kv else params[n["k_norm"]].to(self.q_norm_w.dtype)
         b = None
         if self.qkv_bias:
-            bs = [params["q_proj.bias"], params["k_proj.bias"], params["v_proj.bias"]]
+            bs = [params[n["q_bias"]], params[n["k_bias"]]] + ([] if self.values_are_keys else [params[n["v_bias"]]])
             dt = torch.float32 if any(x.dtype == torch.float32 for x in bs) else bs[0].dtype
             b = torch.cat([x.to(dt) for x in bs]).contiguous()
+            if self.plain_projection:                     # the per-head writer adds it (the product may carry more columns)
+                self.plain_bias, b = b, None
+        if self.sink:
+            self.sinks_dev = params[n["sink"]].to(torch.float32).contiguous()
         self.qkv = Linear(w.contiguous(), b)
         self.o = Linear(params[n["o"]], params.get("o_proj.bias"))
         if self.position is not None:
@@ -170,13 +202,13 @@ class GQAAttention(Mixer):
         keeps_all = self.cache_keeps == "all"
         return KVRequest(self.n_kv_heads, self.head_dim, None if keeps_all else self.window,
                          None if self.v_head_dim == self.head_dim else self.v_head_dim,
-                         None if keeps_all else self.chunk, 0 if keeps_all else self.keep_first)
+                         None if keeps_all else self.chunk, 0 if keeps_all else self.keep_first, self.values_are_keys)
 
     # rows of the query tiles of the two tiled prefill kernels (csrc/attention_prefill.cu, attention_prefill_tc.cu)
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        if self.v_head_dim != self.head_dim:
+        if self.v_head_dim != self.head_dim or self.sink:
             return ()
         return ("attention_tiles128",) if self.keep_first else tuple(self.TILE_ROWS)
 
@@ -216,7 +248,8 @@ class GQAAttention(Mixer):
             y = y.materialize()
         common = dict(compute_dtype=ctx.compute_dtype, rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False),
                       unit_norm_eps=self.qk_norm_eps, q_norm_weight=self.q_norm_w, k_norm_weight=self.k_norm_w,
-                      magnitude=self.magnitude)
+                      magnitude=self.magnitude, bias=self.plain_bias, norm_after_rotation=self.norm_after,
+                      q_temperature=self.q_temperature, values_are_keys=self.values_are_keys)
         writes = view.writes and not self.shares_kv
         args = (self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim, inv_freq, ctx.tok_seq, ctx.tok_pos,
                 ctx.seq_slot, view.block_table, view.k_pages, view.v_pages, writes)
@@ -281,10 +314,11 @@ class GQAAttention(Mixer):
         # kept first positions: the generic kernel, the tcgen05 prompt kernel and the clustered decode kernel walk the
         # pages that hold them before the window's
         kept = dict(keep_first=self.keep_first)
-        if self.v_head_dim != hd or ((self.shaped_scores or self.keep_first) and ctx.compute_dtype != torch.bfloat16):
+        if (self.v_head_dim != hd or self.sink
+                or ((self.shaped_scores or self.keep_first) and ctx.compute_dtype != torch.bfloat16)):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, self.window,
-                                             v_head_dim=self.v_head_dim, **shaped, **kept)
+                                             v_head_dim=self.v_head_dim, sinks=self.sinks_dev, **shaped, **kept)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
             if ctx.options.clustered_decode:

@@ -14,16 +14,28 @@ class PreNormBlock(Block):
     (maeddesg/ROCmForge src/gpu/forward.rs:930-1161; src/cpu/forward.rs:18-337).
 
     ``names`` maps the four parts to their prefixes inside the layer, as the
-    architecture's tensor names have them.
+    architecture's tensor names have them.  ``ffn`` (with ``norm2``) may be None: the block is then its first half.  A
+    mixer made of mixers (``leaf_parts``) brings its leaves' tensors under the joined prefixes.
     """
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward, names: Dict[str, str]):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm = None, ffn: FeedForward = None, names: Dict[str, str] = None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("prenorm block: ffn and norm2 come together or not at all")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.names = dict(names)
 
     def sub_parts(self) -> Dict[str, Part]:
-        return {self.names["norm1"]: self.norm1, self.names["mixer"]: self.mixer,
-                self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn}
+        out = {self.names["norm1"]: self.norm1}
+        out.update(_leaves(self.names["mixer"], self.mixer))
+        if self.ffn is not None:
+            out[self.names["norm2"]] = self.norm2
+            out.update(_leaves(self.names["ffn"], self.ffn))
+        elif self.names.get("norm2") is not None:
+            # a layer without feed-forward: a folder that stores the second norm all the same is not at fault
+            import dataclasses
+            out[""] = UnusedTensors({self.names["norm2"] + local: dataclasses.replace(spec, optional=True)
+                                     for local, spec in self.norm1.param_specs().items()})
+        return out
 
     def entry_norm(self):
         return self.norm1 if self.mixer.accepts_scaled_rows else None
@@ -31,7 +43,14 @@ class PreNormBlock(Block):
     def forward(self, ctx, stream, cache_view):
         after = stream.after_block                   # the norm that follows this block (the model knows the order)
         y = self.norm1.forward(ctx, stream, deferred_ok=self.mixer.accepts_scaled_rows)
-        stream.next_norm = self.norm2 if self.ffn.accepts_scaled_rows else None
+        if self.ffn is None:
+            stream.next_norm = after
+            self.mixer.forward(ctx, y, cache_view, stream)
+            stream.next_norm = None
+            return
+        # a mixer that adds its result to the stream with a kernel of its own may run the next norm in the same pass
+        stream.next_norm = (self.norm2 if self.ffn.accepts_scaled_rows or getattr(self.mixer, "prepares_next_norm", False)
+                            else None)
         self.mixer.forward(ctx, y, cache_view, stream)
         y = self.norm2.forward(ctx, stream, deferred_ok=self.ffn.accepts_scaled_rows)
         stream.next_norm = after

@@ -12,10 +12,12 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """x = E[token], no scaling (maeddesg/ROCmForge src/gpu/forward.rs:826-883)."""
+    """x = E[token], no scaling (maeddesg/ROCmForge src/gpu/forward.rs:826-883); with ``scale``, x = E[token] * scale
+    (formed in 32-bit on the way into the stream; a head tied to the table reads the table itself)."""
 
-    def __init__(self, vocab: int, hidden: int, param_name: str = "weight"):
+    def __init__(self, vocab: int, hidden: int, param_name: str = "weight", scale: Optional[float] = None):
         self.vocab, self.hidden, self.param_name = vocab, hidden, param_name
+        self.scale = None if scale is None or float(scale) == 1.0 else float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -28,11 +30,13 @@ class TokenEmbedding(Part):
         return ["elementwise"]
 
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
-        return kernels.embed(self.weight, token_ids)
+        return kernels.embed(self.weight, token_ids, scale=self.scale)
 
     def forward_with(self, ctx, token_ids: torch.Tensor, positions: "LearnedPositions" = None, rounded: bool = False):
         """(x, y): x = E[token] (+ positions' vector of the token's position), and y = x in the compute dtype if
         ``rounded`` (for a first layer that reads the stream itself), else None; one kernel."""
+        if self.scale is not None:
+            raise NotImplementedError("a scaled embedding does not go with learned positions or a first layer that reads the stream")
         return kernels.embed_positions(self.weight, token_ids, positions.table if positions is not None else None,
                                        ctx.tok_pos if positions is not None else None,
                                        rounded=rounded and ctx.compute_dtype != torch.float32)

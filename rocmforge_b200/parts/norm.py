@@ -14,21 +14,29 @@ from .base import NORMS, Norm
 class RMSNorm(Norm):
     """y_i = x_i * rsqrt(mean(x^2) + eps) * w_i, sums and rsqrt in 32-bit; the weight multiplies
     after normalisation and is used as stored (no 1 + w)
-    (maeddesg/ROCmForge hip_kernels/norm.hip:18-84, src/cpu/ops.rs:32-46)."""
+    (maeddesg/ROCmForge hip_kernels/norm.hip:18-84, src/cpu/ops.rs:32-46).
 
-    def __init__(self, size: int, eps: float, param_name: str = "weight"):
+    ``weight_offset``: for designs that store the weight around zero, y = x * rsqrt(...) * (offset + w); the sum is formed
+    once at load time in 32-bit and the kernels get that 32-bit vector."""
+
+    def __init__(self, size: int, eps: float, param_name: str = "weight", weight_offset: float = 0.0):
         """``param_name``: the weight's name below the part's prefix ("" where the prefix is the tensor's whole name)."""
         self.size = size
         self.eps = float(eps)
+        self.weight_offset = float(weight_offset)
         self.param_name = param_name
         self.weight: Optional[torch.Tensor] = None
         self.compute_dtype = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
+        if self.weight_offset:
+            return {self.param_name: ParamSpec((self.size,), kind="vector", init="normal", std=0.1)}
         return {self.param_name: ParamSpec((self.size,), kind="vector", init="ones")}
 
     def bind(self, params, compute_dtype):
         self.weight = params[self.param_name]
+        if self.weight_offset:
+            self.weight = (self.weight.to(torch.float32) + self.weight_offset).contiguous()
         self.compute_dtype = compute_dtype
 
     def cuda_modules(self, compute_dtype):
