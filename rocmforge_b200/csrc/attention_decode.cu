@@ -333,7 +333,8 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
                               int out_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                               const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
                               int nh, int nkv, float scale, int window, int splits, int* __restrict__ status,
-                              float softcap, const float* __restrict__ slopes, int keep_first) {
+                              float softcap, const float* __restrict__ slopes, int keep_first,
+                              const float* __restrict__ sinks) {
     constexpr int HD = EPL * 32;
     constexpr int NT = WARPS * 32;
     constexpr int HALVES = HD / 64;                             // 128-byte column blocks of a row
@@ -602,7 +603,17 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         float L = 0.f;
 #pragma unroll
         for (int k = 0; k < WARPS; ++k) L += __shfl_sync(0xffffffffu, term, (tid & 31) - w + k);
-        if (w == 0) { c_m[g] = M; c_l[g] = L; }
+        if (w == 0) {
+            // a sink per head: exp(sink) counts once in the denominator, unscaled, with no key and no value; the cluster's
+            // first CTA adds it to its sum (the exponent is bounded so that the sum stays finite: beyond e^80 the row is
+            // zero to every digit anyway)
+            if (sinks != nullptr && rank == 0 && g < G) {
+                const float sk = sinks[kvh * G + g];
+                if (M == -INFINITY) { M = sk; L = 1.f; }
+                else L += expf(fminf(sk - M, 80.f));
+            }
+            c_m[g] = M; c_l[g] = L;
+        }
     }
     __syncthreads();
     const int DS = HD / splits;                          // output dimensions per CTA of the cluster
@@ -693,7 +704,7 @@ static int launch_warps(const void* q, int q_stride, void* out, int out_stride, 
                         const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
                         const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, float scale,
                         int window, int B, int splits, int* status, float softcap, const float* slopes, int keep_first,
-                        cudaStream_t st) {
+                        const float* sinks, cudaStream_t st) {
     constexpr int HD = EPL * 32;
     const size_t smem = (size_t)WARPS * 2 * ROWS * HD * 2 +
                         (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 16 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
@@ -734,7 +745,7 @@ static int launch_warps(const void* q, int q_stride, void* out, int out_stride, 
         return me;
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_warps_kernel<EPL, ROWS, WARPS>, mk, mv,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride, tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status, softcap, slopes, keep_first);
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status, softcap, slopes, keep_first, sinks);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -785,12 +796,13 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
 // A warp per tile of keys, `warps` (4 or 8) warps per CTA.
 // softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
 // lowered by slopes[head] * (query position - key position).  keep_first: with a window (window > 0), the first keep_first
-// positions of a sequence stay visible as well.
-int rf_attention_decode_warps_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                  const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
-                                  const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
-                                  float scale, int window, int B, int splits, int warps, float softcap, const float* slopes,
-                                  int keep_first, int* status, cudaStream_t st) {
+// positions of a sequence stay visible as well.  sinks (float [nh] or null): exp(sinks[head]) counts once in the softmax's
+// denominator, unscaled, with no key and no value.
+int rf_attention_decode_warps_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                   const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                                   const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
+                                   float scale, int window, int B, int splits, int warps, float softcap, const float* slopes,
+                                   int keep_first, const float* sinks, int* status, cudaStream_t st) {
     if (B <= 0) return 0;
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (!rf_attention_decode_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
@@ -799,12 +811,22 @@ int rf_attention_decode_warps_ext(const void* q, int q_stride, void* out, int ou
     if (warps != 4 && warps != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
 #define GOW(EPL, ROWS, WARPS) return launch_warps<EPL, ROWS, WARPS>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, \
-                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, softcap, slopes, keep_first, st)
+                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, softcap, slopes, keep_first, sinks, st)
     if (hd == 64) { if (warps == 8) GOW(2, 32, 8); GOW(2, 32, 4); }
     if (hd == 128) { if (warps == 8) GOW(4, 32, 8); GOW(4, 32, 4); }
     if (warps == 8) GOW(8, 16, 8);
     GOW(8, 16, 4);
 #undef GOW
+}
+
+int rf_attention_decode_warps_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                  const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                                  const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
+                                  float scale, int window, int B, int splits, int warps, float softcap, const float* slopes,
+                                  int keep_first, int* status, cudaStream_t st) {
+    return rf_attention_decode_warps_sink(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, tok_pos, seq_slot,
+                                          block_table, max_pages, nh, nkv, hd, scale, window, B, splits, warps, softcap, slopes,
+                                          keep_first, nullptr, status, st);
 }
 
 int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

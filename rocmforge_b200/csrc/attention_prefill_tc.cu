@@ -87,7 +87,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_start, const int* __restrict__ seq_nnew,
                             const int* __restrict__ cu_q, const int* __restrict__ block_table, int max_pages,
                             int nh, int nkv, float scale, int window, int* __restrict__ status, float softcap,
-                            const float* __restrict__ slopes, int keep_first) {
+                            const float* __restrict__ slopes, int keep_first, const float* __restrict__ sinks) {
     constexpr int HALVES = HD / 64;                     // 128-byte column blocks of a head
     constexpr uint32_t QH_BYTES = AT_BM * 128;          // one column block of the Q tile (also the P tile)
     constexpr uint32_t Q_BYTES = HALVES * QH_BYTES;
@@ -353,6 +353,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && n_kt > 0) ok = mbar_wait(b_pvdone + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, &abort_flag);
         if (ok) {
             tcgen05_fence_after();
+            // a sink per head: exp(sink) counts once in the denominator, unscaled, with no key and no value (a sink far
+            // above the scores makes the sum infinite and the row zero, which is its limit)
+            if (sinks != nullptr && m_ref != -INFINITY) l += at_exp2(fmaf(sinks[head], 1.4426950408889634f, -m_ref));
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* orow = out + (size_t)(row_base + row) * out_stride + (size_t)head * HD;
 #pragma unroll 1
@@ -391,7 +394,7 @@ template <int HD>
 static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
-                     int* status, float softcap, const float* slopes, int keep_first, cudaStream_t st) {
+                     int* status, float softcap, const float* slopes, int keep_first, const float* sinks, cudaStream_t st) {
     constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 15 * 8 + 16;
     static bool configured = false;
     if (!configured) {
@@ -402,7 +405,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     }
     cudaError_t e = rf_launch(attention_prefill_tc_kernel<HD>, dim3(nh, n_tiles), dim3(AT_THREADS), smem, st, mq, mk, mv,
                               reinterpret_cast<__nv_bfloat16*>(out), out_stride, tiles, seq_slot, seq_start, seq_nnew, cu_q,
-                              block_table, max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first);
+                              block_table, max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, sinks);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -419,12 +422,13 @@ int rf_attention_prefill_tc_supported(int nh, int nkv, int hd) {
 // q: [T, q_stride] with the heads' columns first; T is needed for the map's extent.
 // softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
 // lowered by slopes[head] * (query position - key position).  keep_first: with a window (window > 0), the first keep_first
-// positions of a sequence stay visible to every later query as well.
-int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
-                                const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
-                                const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
-                                int max_pages, int nh, int nkv, int hd, float scale, int window, float softcap,
-                                const float* slopes, int keep_first, int* status, cudaStream_t st) {
+// positions of a sequence stay visible to every later query as well.  sinks (float [nh] or null): exp(sinks[head]) counts
+// once in the softmax's denominator, unscaled, with no key and no value.
+int rf_attention_prefill_tc_sink(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
+                                 const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
+                                 const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
+                                 int max_pages, int nh, int nkv, int hd, float scale, int window, float softcap,
+                                 const float* slopes, int keep_first, const float* sinks, int* status, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) return RF_ERR_BAD_ARG;
     if (n_tiles > 65535) return RF_ERR_UNSUPPORTED;      // tiles are the grid's y dimension (8 million prompt tokens)
@@ -438,9 +442,19 @@ int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, i
         return e;
     if (hd == 64)
         return at_launch<64>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                             max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, st);
+                             max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, sinks, st);
     return at_launch<128>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                          max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, st);
+                          max_pages, nh, nkv, scale, window, status, softcap, slopes, keep_first, sinks, st);
+}
+
+int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
+                                const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
+                                const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
+                                int max_pages, int nh, int nkv, int hd, float scale, int window, float softcap,
+                                const float* slopes, int keep_first, int* status, cudaStream_t st) {
+    return rf_attention_prefill_tc_sink(q, q_stride, T, out, out_stride, k_pages, v_pages, n_pages, tiles, n_tiles, seq_slot,
+                                        seq_start, seq_nnew, cu_q, block_table, max_pages, nh, nkv, hd, scale, window, softcap,
+                                        slopes, keep_first, nullptr, status, st);
 }
 
 int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,

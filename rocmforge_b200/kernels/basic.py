@@ -517,11 +517,12 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
                            tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                            splits: int | None = None, warps: int | None = None,
                            out: torch.Tensor | None = None, *, softcap: float | None = None,
-                           slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                           slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
+                           sinks: torch.Tensor | None = None) -> torch.Tensor:
     """One new token per sequence over the bfloat16 paged cache: a cluster of ``splits`` CTAs per (sequence,
     kv head), every warp on its own tiles of keys; merged through distributed shared memory.  ``warps``
-    per CTA: 8 while one CTA per SM is enough for the batch, else 4 (three CTAs fit an SM).  ``softcap``, ``slopes`` and
-    ``keep_first`` as in ``attention_generic``."""
+    per CTA: 8 while one CTA per SM is enough for the batch, else 4 (three CTAs fit an SM).  ``softcap``, ``slopes``,
+    ``keep_first`` and ``sinks`` as in ``attention_generic``."""
     need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table)
     B = q.shape[0]
     need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1, "attention_decode: q must be bfloat16 [B, ...]")
@@ -540,14 +541,16 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
     from .tensor_core import status_word
     need(slopes is None or (slopes.is_cuda and slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
          "attention_decode: slopes must be float32 [heads]")
-    f = _f("attention_decode", "rf_attention_decode_warps_ext", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    need(sinks is None or (sinks.is_cuda and sinks.dtype == torch.float32 and sinks.shape == (n_heads,) and sinks.is_contiguous()),
+         "attention_decode: sinks must be float32 [heads]")
+    f = _f("attention_decode", "rf_attention_decode_warps_sink", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
            c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-           c_float, c_void_p, c_int, c_void_p, c_void_p)
+           c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p)
     span = key_span(window, chunk)
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(tok_seq),
             ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim,
             float(scale), span, B, splits, warps, float(softcap or 0.0), ptr(slopes),
-            int(keep_first or 0) if span > 0 else 0, ptr(status_word(q.device)), stream()),
+            int(keep_first or 0) if span > 0 else 0, ptr(sinks), ptr(status_word(q.device)), stream()),
           f"attention_decode_warps (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
     return out
 
@@ -563,11 +566,14 @@ def attention_prefill_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int)
 def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                          q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
                          window: int | None, out: torch.Tensor | None = None, *, softcap: float | None = None,
-                         slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                         slopes: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
+                         sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products as tcgen05.mma (accumulators in tensor
-    memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles.  ``softcap``, ``slopes`` and ``keep_first``
-    as in ``attention_generic``."""
-    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table, slopes)
+    memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles.  ``softcap``, ``slopes``, ``keep_first`` and
+    ``sinks`` as in ``attention_generic``."""
+    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table, slopes, sinks)
+    need(sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (n_heads,) and sinks.is_contiguous()),
+         "attention_prefill_tc: sinks must be float32 [heads]")
     need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
          "attention_prefill_tc: slopes must be float32 [heads]")
     T = q.shape[0]
@@ -583,14 +589,14 @@ def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     if out is None:
         out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     from .tensor_core import status_word
-    f = _f("attention_prefill_tc", "rf_attention_prefill_tc_ext", c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    f = _f("attention_prefill_tc", "rf_attention_prefill_tc_sink", c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
            c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-           c_int, c_float, c_void_p, c_int, c_void_p, c_void_p)
+           c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p)
     span = key_span(window, chunk)
     check(f(ptr(q), q.stride(0), T, ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
             q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
             block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), span, float(softcap or 0.0),
-            ptr(slopes), int(keep_first or 0) if span > 0 else 0, ptr(status_word(q.device)), stream()),
+            ptr(slopes), int(keep_first or 0) if span > 0 else 0, ptr(sinks), ptr(status_word(q.device)), stream()),
           f"attention_prefill_tc (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
 

@@ -192,7 +192,7 @@ class GQAAttention(Mixer):
         mods = ["elementwise", "attention_generic"]
         if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim:
             mods += ["attention_decode", "attention_prefill_tc"]
-            if not self.shaped_scores and not self.keep_first:
+            if not self.shaped_scores and not self.keep_first and not self.sink:
                 mods.append("attention_prefill")         # the mma.sync prompt kernel knows no cap and no slopes
         return mods
 
@@ -208,9 +208,9 @@ class GQAAttention(Mixer):
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        if self.v_head_dim != self.head_dim or self.sink:
+        if self.v_head_dim != self.head_dim:
             return ()
-        return ("attention_tiles128",) if self.keep_first else tuple(self.TILE_ROWS)
+        return ("attention_tiles128",) if self.keep_first or self.sink else tuple(self.TILE_ROWS)
 
     def step_table(self, name, batch):
         """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
@@ -314,11 +314,12 @@ class GQAAttention(Mixer):
         # kept first positions: the generic kernel, the tcgen05 prompt kernel and the clustered decode kernel walk the
         # pages that hold them before the window's
         kept = dict(keep_first=self.keep_first)
-        if (self.v_head_dim != hd or self.sink
-                or ((self.shaped_scores or self.keep_first) and ctx.compute_dtype != torch.bfloat16)):
+        shaped["sinks"] = self.sinks_dev                  # (None without): known to the same kernels as a cap and slopes
+        if (self.v_head_dim != hd
+                or ((self.shaped_scores or self.keep_first or self.sink) and ctx.compute_dtype != torch.bfloat16)):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, self.window,
-                                             v_head_dim=self.v_head_dim, sinks=self.sinks_dev, **shaped, **kept)
+                                             v_head_dim=self.v_head_dim, **shaped, **kept)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
             if ctx.options.clustered_decode:
@@ -328,7 +329,8 @@ class GQAAttention(Mixer):
                     q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                     view.block_table, self.scale, self.window,
                     splits=kernels.decode_splits(ctx.B, nkv, longest, span), **shaped, **kept)
-            if not self.shaped_scores and not self.keep_first and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
+            if (not self.shaped_scores and not self.keep_first and not self.sink
+                    and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK):
                 # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
                 max_chunks = 1
@@ -352,7 +354,7 @@ class GQAAttention(Mixer):
             return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles128,
                                                 ctx.seq_slot, ctx.seq_start, ctx.seq_nnew, ctx.cu_q,
                                                 view.block_table, self.scale, self.window, **shaped, **kept)
-        if self.shaped_scores or self.keep_first:
+        if self.shaped_scores or self.keep_first or self.sink:
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, self.window, **shaped, **kept)
         if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention

@@ -26,15 +26,17 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def folders(tmp_path_factory):
     """Factory: (config name, dtype) -> model folder with random weights, made once per session."""
-    from helpers import (CONFIGS, FIGALIX_CONFIGS, RIFIZEN_CONFIGS, VILULORN_CONFIGS, write_figalix, write_rifizen, write_tiny,
-                         write_vilulorn)
+    from helpers import (CONFIGS, FIGALIX_CONFIGS, LUDUSUN_CONFIGS, RIFIZEN_CONFIGS, VILULORN_CONFIGS, write_figalix,
+                         write_ludusun, write_rifizen, write_tiny, write_vilulorn)
     made = {}
 
     def get(name: str, dtype: str = "float32") -> str:
         key = (name, dtype)
         if key not in made:
             d = tmp_path_factory.mktemp(f"model_{name}_{dtype}")
-            if name in FIGALIX_CONFIGS:
+            if name in LUDUSUN_CONFIGS:
+                write_ludusun(LUDUSUN_CONFIGS[name], str(d), dtype)
+            elif name in FIGALIX_CONFIGS:
                 write_figalix(FIGALIX_CONFIGS[name], str(d), dtype)
             elif name in VILULORN_CONFIGS:
                 write_vilulorn(VILULORN_CONFIGS[name], str(d), dtype)

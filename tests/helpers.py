@@ -354,3 +354,95 @@ def write_figalix(cfg: dict, folder: str, dtype: str = "float32") -> None:
     c, raw = figalix_config(cfg)
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     rf.write_model_folder(folder, raw, architecture_for("Figalix").build(c).param_specs(), cfg["seed"], dt)
+
+
+# --------------------------------------------------------------------------- Ludusun
+
+def _sink_attention(*, heads, kv_heads, dim, vdim, scale, rot_dims=0, rot_base=None, scaling=None, kv_from=None, mlp):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot_dims:
+        m["rot"] = {"dims": rot_dims, "base": rot_base}
+        if scaling is not None:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def _latent(*, heads, dim, vdim, q_rank, kv_rank, scale, window=None, mlp):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale}
+    if window is not None:
+        m["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def _summed(*, heads, kv_heads, dim, scale, q_temp=None, r_heads, r_kv_heads, r_dim, r_vdim, conv, left_scale, right_scale, mlp):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale}
+    if q_temp is not None:
+        left["q_temp"] = {"coef": q_temp[0], "every": q_temp[1]}
+    right = {"heads": r_heads, "kv_heads": r_kv_heads, "dim": r_dim, "vdim": r_vdim, "conv": conv}
+    return {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale},
+            "mlp": mlp}
+
+
+# Sizes that differ from each other in every respect: which kind of layer comes first, values of another size than keys,
+# one kv head for nine and for sixteen heads and as many as heads, heads rotated wholly, partly (with and without the ramp
+# of stretched frequencies) and not at all, layers that read an earlier layer's keys, latents narrower and wider than the
+# heads they expand to, windows of 7, 33, 70, 100, 130 and none, a query temperature that steps every position, every 5 and
+# every 64 positions and none, delta-rule heads that share q and k and heads with their own, 1 to 7 taps, low ranks of 1 to
+# 24 (no multiple of 8 among them), a state of 256 x 8, layers without feed-forward, an embedding scale of 1 and others,
+# branch factors of 1 and others, logits capped and not, a width that no tensor-core kernel takes.  ``ranks``: rows of the
+# delta rule's two narrow matrices (a tensor's shape, not a key of the design).
+LUDUSUN_A = dict(seed=41, architecture="Ludusun", vocab=96, width=64, norm={"eps": 1e-5}, embedding={"scale": 2.0},
+                 logit_softcap=8.0, ranks={"l0.mix.right.a1": 5, "l0.mix.right.g1": 3},
+                 layers=[_summed(heads=4, kv_heads=2, dim=16, scale=0.25, q_temp=(0.3, 5), r_heads=2, r_kv_heads=1, r_dim=24,
+                                 r_vdim=12, conv=3, left_scale=1.0, right_scale=0.7, mlp=_dense(40)),
+                         _sink_attention(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.3, rot_dims=8, rot_base=100.0,
+                                         scaling=(4.0, 16, 4.0, 1.0), mlp=None),
+                         _latent(heads=3, dim=8, vdim=16, q_rank=12, kv_rank=20, scale=0.35, window=7, mlp=_dense(48)),
+                         _sink_attention(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.5, rot_dims=8, rot_base=100.0,
+                                         scaling=(4.0, 16, 4.0, 1.0), kv_from=1, mlp=_dense(24))])
+LUDUSUN_B = dict(seed=42, architecture="Ludusun", vocab=200, width=128, norm={"eps": 1e-6}, embedding={"scale": 1.0},
+                 ranks={"l2.mix.right.a1": 16, "l2.mix.right.g1": 9},
+                 layers=[_sink_attention(heads=9, kv_heads=1, dim=20, vdim=12, scale=0.2, rot_dims=6, rot_base=1e6, mlp=_dense(100)),
+                         _latent(heads=2, dim=40, vdim=40, q_rank=8, kv_rank=64, scale=0.16, window=70, mlp=None),
+                         _summed(heads=3, kv_heads=3, dim=40, scale=0.16, r_heads=4, r_kv_heads=2, r_dim=64, r_vdim=32, conv=1,
+                                 left_scale=0.5, right_scale=1.0, mlp=_dense(64)),
+                         _sink_attention(heads=9, kv_heads=1, dim=20, vdim=12, scale=0.3, rot_dims=6, rot_base=1e6, kv_from=0,
+                                         mlp=_dense(40)),
+                         _latent(heads=1, dim=24, vdim=8, q_rank=30, kv_rank=16, scale=0.2, window=130, mlp=_dense(32))])
+LUDUSUN_C = dict(seed=43, architecture="Ludusun", vocab=300, width=256, norm={"eps": 1e-6}, embedding={"scale": 4.0},
+                 logit_softcap=30.0, ranks={"l2.mix.right.a1": 24, "l2.mix.right.g1": 12},
+                 layers=[_latent(heads=4, dim=64, vdim=64, q_rank=96, kv_rank=136, scale=0.125, window=100, mlp=_dense(320)),
+                         _sink_attention(heads=8, kv_heads=2, dim=64, vdim=64, scale=0.125, rot_dims=32, rot_base=1e6,
+                                         scaling=(4.0, 256, 16.0, 2.0), mlp=_dense(128)),
+                         _summed(heads=8, kv_heads=2, dim=64, scale=0.125, q_temp=(0.5, 64), r_heads=4, r_kv_heads=2, r_dim=32,
+                                 r_vdim=48, conv=2, left_scale=0.8, right_scale=0.5, mlp=_dense(96)),
+                         _sink_attention(heads=8, kv_heads=2, dim=64, vdim=64, scale=0.2, rot_dims=32, rot_base=1e6,
+                                         scaling=(4.0, 256, 16.0, 2.0), kv_from=1, mlp=None),
+                         _sink_attention(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, rot_dims=128, rot_base=1e4,
+                                         mlp=_dense(64)),
+                         _latent(heads=2, dim=128, vdim=128, q_rank=64, kv_rank=32, scale=0.09, window=33, mlp=_dense(64))])
+LUDUSUN_D = dict(seed=44, architecture="Ludusun", vocab=130, width=100, norm={"eps": 1e-6}, embedding={"scale": 0.5},
+                 logit_softcap=2.0, ranks={"l0.mix.right.a1": 1, "l0.mix.right.g1": 2},
+                 layers=[_summed(heads=16, kv_heads=1, dim=64, scale=0.125, q_temp=(1.0, 1), r_heads=1, r_kv_heads=1, r_dim=256,
+                                 r_vdim=8, conv=7, left_scale=0.3, right_scale=2.0, mlp=None),
+                         _sink_attention(heads=2, kv_heads=2, dim=64, vdim=128, scale=0.3, mlp=_dense(24)),
+                         _latent(heads=16, dim=16, vdim=24, q_rank=7, kv_rank=9, scale=0.25, mlp=_dense(16))])
+LUDUSUN_CONFIGS = {"LA": LUDUSUN_A, "LB": LUDUSUN_B, "LC": LUDUSUN_C, "LD": LUDUSUN_D}
+
+
+def ludusun_config(cfg: dict):
+    """(typed configuration, the dict that goes into config.json)."""
+    from rocmforge_b200.config import architecture_for
+    raw = {k: v for k, v in cfg.items() if k not in ("seed", "ranks")}
+    shapes = {name: (r, cfg["width"]) for name, r in cfg.get("ranks", {}).items()}
+    return architecture_for("Ludusun").config_cls.from_dict(raw, shapes=shapes), raw
+
+
+def write_ludusun(cfg: dict, folder: str, dtype: str = "float32") -> None:
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import architecture_for
+    c, raw = ludusun_config(cfg)
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    rf.write_model_folder(folder, raw, architecture_for("Ludusun").build(c).param_specs(), cfg["seed"], dt)
