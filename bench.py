@@ -472,6 +472,30 @@ def figalix_shape(width, layers=4):
     return fig, rifizen_shape(width, layers)[0]
 
 
+def ludusun_shape(width, layers=4):
+    """A Ludusun configuration with layers of the size a real model has, all heads of 128: attention over all earlier
+    positions with a sink per head, wholly rotated heads with stretched frequencies and a quarter as many kv heads; latent
+    attention over a window of 1,024 (queries from a latent of width / 2, keys and values from one of 512); attention
+    whose values are its keys with a query temperature beside the gated delta rule with a state of 128 x 128 per head and 4
+    taps; and attention on the first layer's keys; a dense feed-forward of 4 x width everywhere.  And the Figalix
+    configuration of equal width, heads and depth with dense feed-forwards (its closest relative here: attention beside a
+    matrix state per head, rotate-half pairs with stretched frequencies, sigmoid gates, a tied head with capped logits)."""
+    heads = width // 128
+    kvh = max(1, heads // 4)
+    rot = dict(dims=128, base=1e6, scaling=dict(factor=8.0, original=8192, fast=32.0, slow=1.0))
+    att = dict(heads=heads, kv_heads=kvh, dim=128, vdim=128, scale=128 ** -0.5, rot=rot)
+    lat = dict(heads=heads, dim=128, vdim=128, q_rank=width // 2, kv_rank=512, scale=128 ** -0.5, mask={"size": 1024})
+    par = dict(left=dict(heads=heads, kv_heads=kvh, dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.1, every=256)),
+               right=dict(heads=heads, kv_heads=heads, dim=128, vdim=128, conv=4), left_scale=0.7, right_scale=0.7)
+    kinds = [("attention", att), ("latent_attention", lat), ("parallel", par), ("attention", dict(att, kv_from=0))]
+    dense = dict(kind="dense", ff=4 * width)
+    lud = dict(architecture="Ludusun", vocab=32000, width=width, norm=dict(eps=1e-6), embedding=dict(scale=2.0), logit_softcap=30.0,
+               layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=dense) for i in range(layers)])
+    fig = figalix_shape(width, layers)[0]
+    fig = dict(fig, layers=[dict(L, mlp=dense) for L in fig["layers"]])
+    return lud, fig
+
+
 def rifizen_points(pk, seed, widths=(1024, 2048), tokens=PREFILL_TOKENS, batches=(8, 64), steps=64, warmup=8,
                    names=("rifizen", "dense"), archs=("Rifizen", "Qwen2ForCausalLM"), shapes=None):
     """Prefill and decode of one design at layer sizes of a real model, beside another at equal size (by default Rifizen
@@ -585,7 +609,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen", "vilulorn", "figalix"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen", "vilulorn", "figalix", "ludusun"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
                     help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
@@ -625,6 +649,12 @@ def main():
                           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
                           **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup, names=("figalix", "rifizen"),
                                            archs=("Figalix", "Rifizen"), shapes=figalix_shape)}))
+        return 0
+    if args.only == "ludusun":
+        print(json.dumps({"only": "ludusun", "tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
+                          "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
+                          **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup, names=("ludusun", "figalix"),
+                                           archs=("Ludusun", "Figalix"), shapes=ludusun_shape)}))
         return 0
     if args.only in ("0.5b", "14b"):
         print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))

@@ -1297,12 +1297,14 @@ def delta_prepare(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_l
 
 def delta_scan(qn: torch.Tensor, kn: torch.Tensor, kq: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, v: torch.Tensor,
                state: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor, heads: int, qk_heads: int, dim: int,
-               vdim: int) -> torch.Tensor:
+               vdim: int, one_token: bool = False, lanes: int = 0) -> torch.Tensor:
     """The gated delta rule, token by token for every sequence of the step, per head (head h reads q/k head h // (heads /
     qk_heads)):  S <- diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t.
 
     ``state`` float32 [slots, heads, dim, vdim] is read and replaced; ``v`` float32 [T, >= heads*vdim] view; returns o float32
-    [T, heads*vdim].  The sums' order depends on (dim, position) alone."""
+    [T, heads*vdim].  The sums' order depends on (dim, position) alone.  ``one_token``: every sequence of the
+    step brings exactly one token (the kernel form for decoding: four lanes a value column instead of eight, which adds a
+    column's products in another order; ``lanes`` 4 or 8 forces a form, for measurements)."""
     need_cuda(qn, kn, kq, decay, beta, v, state, cu_q, seq_slot)
     T = qn.shape[0]
     B = seq_slot.shape[0]
@@ -1314,7 +1316,7 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, kq: torch.Tensor, decay: torc
     need(dim <= 256, "delta_scan: at most 256 key channels a head")
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qn.device)
     f = _f("delta", "rf_delta_scan", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p)
+           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p)
     check(f(ptr(qn), ptr(kn), ptr(kq), ptr(decay), ptr(beta), ptr(v), v.stride(0), ptr(state), ptr(o), ptr(cu_q), ptr(seq_slot),
-            B, heads, qk_heads, dim, vdim, stream()), f"delta_scan (heads={heads}, dim={dim}, vdim={vdim})")
+            B, heads, qk_heads, dim, vdim, int(bool(one_token)), int(lanes), stream()), f"delta_scan (heads={heads}, dim={dim}, vdim={vdim})")
     return o

@@ -29,7 +29,8 @@ class GatedDeltaRule(Mixer):
     One product makes q | k | v | W_b x | W_a1 x | W_g1 x in the compute dtype; the decay's second product stays 32-bit,
     and so do the convolution's result, the unit norms, beta, softplus, the decays, S, o and its norm.  Per sequence the
     mixer keeps S [heads, dim, vdim] and the convolution's last taps-1 inputs, so a prompt may be cut anywhere; the
-    recurrence runs token by token in prompts too, so its sums do not depend on the cut.
+    recurrence runs token by token in prompts too, so its sums do not depend on how a prompt is cut into portions (a token
+    decoded alone takes another kernel form, whose sums differ by rounding).
     ``names``: the tensors' names below the part's prefix (keys q, k, v, q_conv, k_conv, v_conv, b, a_log, dt_bias, a1, a2,
     g1, g2, norm, o).
     """
@@ -141,7 +142,7 @@ class GatedDeltaRule(Mixer):
         qn, kn, kq, decay, beta = kernels.delta_prepare(qkv, a, self.dt_bias, self.a_log, p[:, c["b"]:c["b"] + self.n_heads],
                                                         self.n_heads, self.qk_heads, self.dim, self.q_scale, self.unit_eps)
         o = kernels.delta_scan(qn, kn, kq, decay, beta, qkv[:, 2 * self.qk_size:], state_view["S"], ctx.cu_q, ctx.seq_slot,
-                               self.n_heads, self.qk_heads, self.dim, self.vdim)
+                               self.n_heads, self.qk_heads, self.dim, self.vdim, one_token=ctx.is_decode)
         return kernels.retention_gate(o, gate, self.n_heads, self.vdim, self.eps, weight=self.norm_w, gate_fn="sigmoid")
 
     def forward(self, ctx, y, cache_view, stream):

@@ -478,8 +478,8 @@ def _steps(lengths_per_step):
 def test_delta_rule_kernels(heads, qk_heads, dim, vdim):
     """The prepared inputs (unit vectors, k . q, decays, beta) and the recurrence against the plain functions: two sequences
     in slots 2 and 0 over four steps (a long portion, a short one, single tokens), a slot zeroed and used again, decays of
-    exactly 1 (a channel that never forgets) and of 0 (one that forgets at once), beta of 0 and 1; and the same bits
-    however the tokens are cut into steps."""
+    exactly 1 (a channel that never forgets) and of 0 (one that forgets at once), beta of 0 and 1; the same bits however
+    the tokens are cut into steps; and the form for steps of one token a sequence against the general one."""
     from rocmforge_b200 import kernels
     dev = "cuda"
     torch.manual_seed(heads * 1000 + dim)
@@ -517,7 +517,7 @@ def test_delta_rule_kernels(heads, qk_heads, dim, vdim):
             outs.append(o); states.append(S)
         return torch.stack(outs, dim=1), torch.stack(states)
 
-    def run(plan):
+    def run(plan, one_token=False):
         state = torch.full((3, H, D, V), float("nan"), device=dev)
         state[[0, 2]] = 0.0
         at = {s: 0 for s in total}
@@ -526,7 +526,7 @@ def test_delta_rule_kernels(heads, qk_heads, dim, vdim):
             parts = [tuple(x[at[s]: at[s] + n] for x in data[s]) for s, n in step]
             qkv, a, bsrc = (torch.cat([p[i] for p in parts]).contiguous() for i in range(3))
             qn, kn, kq, decay, beta = kernels.delta_prepare(qkv, a, dt_bias, a_log, bsrc, H, G, D, q_scale, 1e-6)
-            o = kernels.delta_scan(qn, kn, kq, decay, beta, qkv[:, 2 * G * D:], state, cu, slots, H, G, D, V)
+            o = kernels.delta_scan(qn, kn, kq, decay, beta, qkv[:, 2 * G * D:], state, cu, slots, H, G, D, V, one_token=one_token)
             row = 0
             for s, n in step:
                 outs[s].append(o[row: row + n]); row += n; at[s] += n
@@ -545,6 +545,11 @@ def test_delta_rule_kernels(heads, qk_heads, dim, vdim):
     for slot in total:
         assert torch.equal(got[slot], got1[slot]) and torch.equal(got[slot], got2[slot]), "the cut changes the outputs' bits"
         assert torch.equal(state[slot], state1[slot]) and torch.equal(state[slot], state2[slot])
+    # the kernel form of decoding (one token a sequence) adds a column's products in another order: equal up to rounding
+    got3, state3 = run(single, one_token=True)
+    for slot in total:
+        assert (got3[slot] - got[slot]).abs().max() < 1e-5 * max(1.0, float(got[slot].abs().max()))
+        assert (state3[slot] - state[slot]).abs().max() < 1e-5 * max(1.0, float(state[slot].abs().max()))
 
 
 def test_the_sum_of_two_branches_and_the_norm_after_it():
