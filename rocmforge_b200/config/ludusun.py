@@ -119,6 +119,14 @@ class LudusunConfig:
             def g(path, k, L=L, p=p, **kw):
                 return _get(L, path, k, where=p + ".", **kw)
             if kind == "attention":
+                # a layer that reads another layer's keys and values may leave out what it shares with that layer
+                src = L.get("mixer", {}).get("kv_from") if isinstance(L.get("mixer"), dict) else None
+                if isinstance(src, int) and not isinstance(src, bool) and 0 <= src < i and isinstance(layers_raw[src].get("mixer"), dict):
+                    L = dict(L, mixer={**{k: v for k, v in layers_raw[src]["mixer"].items() if k in ("kv_heads", "dim", "vdim", "rot")},
+                                       **L["mixer"]})
+
+                    def g(path, k, L=L, p=p, **kw):
+                        return _get(L, path, k, where=p + ".", **kw)
                 mixer = cls._attention(L, g, p, i, layers)
             elif kind == "latent_attention":
                 mixer = LatentAttentionConfig(
@@ -196,8 +204,8 @@ class LudusunConfig:
             src = layers[j] if j < i else None
             if src is None or src.type != "attention" or src.mixer.kv_from is not None:
                 raise InvalidValue(f"{p}.mixer.kv_from", j, "must name an earlier attention layer with keys and values of its own")
-            if not all(getattr(src.mixer, k) == getattr(m, k) for k in ("kv_heads", "dim", "vdim", "rot_dims", "rot_base", "rot_scaling")):
-                raise InvalidValue(f"{p}.mixer.kv_from", j, "the two layers' kv heads, head sizes and rotation must be equal")
+            if not all(getattr(src.mixer, k) == getattr(m, k) for k in ("kv_heads", "dim", "vdim")):
+                raise InvalidValue(f"{p}.mixer.kv_from", j, "the two layers' kv heads and head sizes must be equal")
         return m
 
     def to_dict(self) -> dict:

@@ -26,7 +26,8 @@ delta_prepare_kernel(const float* __restrict__ qkv, int qkv_stride, const float*
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     pdl_wait();
     const float* row = qkv + (size_t)t * qkv_stride;
-    for (int g = warp; g < G; g += nwarp) {                 // a warp per q/k head
+    // few tokens: a token's heads and channels are spread over gridDim.y blocks
+    for (int g = blockIdx.y * nwarp + warp; g < G; g += gridDim.y * nwarp) {                 // a warp per q/k head
         const float* q = row + g * D;
         const float* k = row + (G + g) * D;
         float sq = 0.f, sk = 0.f, dot = 0.f;
@@ -39,13 +40,13 @@ delta_prepare_kernel(const float* __restrict__ qkv, int qkv_stride, const float*
         }
         if (lane == 0) kq[(size_t)t * G + g] = dot * rq * rk;
     }
-    for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H * D; i += gridDim.y * blockDim.x) {
         const int h = i / D;
         const float x = a[(size_t)t * H * D + i] + load_vec(dt_bias, vec_is_f32, i);
         const float sp = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
         decay[(size_t)t * H * D + i] = expf(-expf(load_vec(a_log, vec_is_f32, h)) * sp);
     }
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
+    for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < H; h += gridDim.y * blockDim.x)
         beta[(size_t)t * H + h] = 1.f / (1.f + expf(-Cvt<T>::to_f32(beta_src[(size_t)t * beta_stride + h])));
 }
 
@@ -204,11 +205,13 @@ int rf_delta_prepare(int dtype, const float* qkv, int qkv_stride, const float* a
                      float* beta, int H, int G, int D, float q_scale, float unit_eps, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0) return RF_ERR_BAD_ARG;
+    int by = T_ >= 512 ? 1 : (H * D + 511) / 512;           // about four decays a thread when there are few tokens
+    if (by > 32) by = 32;
     if (dtype == 0)
-        rf_launch(delta_prepare_kernel<float>, dim3(T_), dim3(128), 0, st, qkv, qkv_stride, a, dt_bias, a_log, vec_is_f32,
+        rf_launch(delta_prepare_kernel<float>, dim3(T_, by), dim3(128), 0, st, qkv, qkv_stride, a, dt_bias, a_log, vec_is_f32,
                   reinterpret_cast<const float*>(beta_src), beta_stride, qn, kn, kq, decay, beta, H, G, D, q_scale, unit_eps);
     else
-        rf_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T_), dim3(128), 0, st, qkv, qkv_stride, a, dt_bias, a_log, vec_is_f32,
+        rf_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T_, by), dim3(128), 0, st, qkv, qkv_stride, a, dt_bias, a_log, vec_is_f32,
                   reinterpret_cast<const __nv_bfloat16*>(beta_src), beta_stride, qn, kn, kq, decay, beta, H, G, D, q_scale, unit_eps);
     RF_LAUNCH_CHECK();
     return 0;
