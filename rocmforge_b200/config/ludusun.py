@@ -57,7 +57,7 @@ class KeyValueAttentionConfig:
     dim: int
     vdim: int
     scale: float
-    q_temp: Optional[Tuple[float, int]]
+    q_temp: Optional[Tuple[float, float]]
 
 
 @dataclass
@@ -142,7 +142,7 @@ class LudusunConfig:
                     return int(ranks.get(key, cls.DEFAULT_RANK))
                 qt = None
                 if isinstance(L.get("mixer", {}).get("left", {}).get("q_temp"), dict):
-                    qt = (g("mixer.left.q_temp.coef", float), g("mixer.left.q_temp.every", int, minimum=1))
+                    qt = (g("mixer.left.q_temp.coef", float), g("mixer.left.q_temp.every", float, positive=True))
                 left = KeyValueAttentionConfig(
                     heads=g("mixer.left.heads", int, minimum=1), kv_heads=g("mixer.left.kv_heads", int, minimum=1),
                     dim=g("mixer.left.dim", int, minimum=1), vdim=g("mixer.left.vdim", int, minimum=1),

@@ -29,6 +29,8 @@ def _get(raw: dict, path: str, kind, *, optional=False, minimum=None, positive=F
             raise MissingKey(where + path)
         cur = cur[part]
     path = where + path
+    if kind is int and isinstance(cur, float) and cur.is_integer():
+        cur = int(cur)                      # a whole number written with a decimal point
     if isinstance(cur, bool) or not isinstance(cur, (int, float) if kind is float else int):
         raise InvalidValue(path, cur, "must be a number" if kind is float else "must be an integer")
     if minimum is not None and cur < minimum:

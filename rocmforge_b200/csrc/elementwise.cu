@@ -578,7 +578,7 @@ struct HeadWriteExtras {
     int bias_is_f32;
     int norm_after;
     float q_coef;
-    int q_every;
+    float q_every;
     int v_is_k;
 };
 
@@ -603,7 +603,7 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
     const int page = write_kv ? block_table[(size_t)slot * max_pages + pos / RF_PAGE] : 0;
     const int rh = rot_dim >> 1;
     // a query's temperature grows with its position in steps of q_every positions
-    const float q_temp = ex.q_every > 0 ? 1.f + ex.q_coef * logf((float)((pos + 1) / ex.q_every) + 1.f) : 1.f;
+    const float q_temp = ex.q_every > 0.f ? 1.f + ex.q_coef * logf(floorf((float)(pos + 1) / ex.q_every) + 1.f) : 1.f;
     pdl_wait();
     const int n_heads_all = write_kv ? nh + (ex.v_is_k ? 1 : 2) * nkv : nh;
     for (int head = blockIdx.y * nwarp + warp; head < n_heads_all; head += gridDim.y * nwarp) {
@@ -1135,9 +1135,9 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
                                      int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, int rot_dim,
                                      int interleaved, int unit_norm, float eps, cudaStream_t st,
                                      const void* q_norm_w = nullptr, const void* k_norm_w = nullptr, int norm_w_is_f32 = 0,
-                                     float magnitude = 1.f, HeadWriteExtras ex = HeadWriteExtras{nullptr, 0, 0, 0.f, 0, 0}) {
+                                     float magnitude = 1.f, HeadWriteExtras ex = HeadWriteExtras{nullptr, 0, 0, 0.f, 0.f, 0}) {
     if (T_ <= 0) return 0;
-    if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0 || ex.q_every < 0) return RF_ERR_BAD_ARG;
+    if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0 || ex.q_every < 0.f) return RF_ERR_BAD_ARG;
     const size_t smem = (size_t)4 * 2 * (hd > hdv ? hd : hdv) * sizeof(float);
     if (smem > 48 * 1024) return RF_ERR_UNSUPPORTED;
     // few tokens: a token's heads over several blocks (a warp per head)
@@ -1254,7 +1254,7 @@ int rf_head_norm_kv_write_x(int dtype, const void* src, int row_stride, int n_pa
                             const int* tok_pos, const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
                             void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, int unit_norm, float eps,
                             const void* q_norm_w, const void* k_norm_w, int norm_w_is_f32, float magnitude,
-                            const void* bias, int bias_is_f32, int norm_after, float q_coef, int q_every, int v_is_k,
+                            const void* bias, int bias_is_f32, int norm_after, float q_coef, float q_every, int v_is_k,
                             cudaStream_t st) {
     const HeadWriteExtras ex{bias, bias_is_f32, norm_after, q_coef, q_every, v_is_k};
     return dtype == 0

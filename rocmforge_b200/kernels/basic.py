@@ -711,11 +711,11 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         need_cuda(bias)
         need(bias is None or (bias.shape == (width,) and bias.is_contiguous() and bias.dtype in (torch.float32, torch.bfloat16)),
              "head_norm_kv_write: the bias must be [width] in float32 or bfloat16")
-        coef, every = (float(q_temperature[0]), int(q_temperature[1])) if q_temperature is not None else (0.0, 0)
-        need(q_temperature is None or every >= 1, "head_norm_kv_write: the temperature's step must be at least one position")
+        coef, every = (float(q_temperature[0]), float(q_temperature[1])) if q_temperature is not None else (0.0, 0.0)
+        need(q_temperature is None or every > 0, "head_norm_kv_write: the temperature's step must be a positive number of positions")
         f = _f("elementwise", "rf_head_norm_kv_write_x", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
                c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-               c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p)
+               c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p)
         check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(q_out), q_out.stride(0), n_heads, n_kv_heads, head_dim,
                 v_head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
                 ptr(k_pages), ptr(None if values_are_keys else v_pages), int(write_kv), T, int(rot_dim), int(interleaved),

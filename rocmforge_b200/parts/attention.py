@@ -98,9 +98,9 @@ class GQAAttention(Mixer):
         self.norm_after = bool(qk_norm_after_rotation)
         if self.norm_after and qk_norm_eps is None:
             raise ValueError("gqa_attention: qk_norm_after_rotation goes with qk_norm_eps")
-        self.q_temperature = None if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
-        if self.q_temperature is not None and self.q_temperature[1] < 1:
-            raise ValueError("gqa_attention: the query temperature's step must be at least one position")
+        self.q_temperature = None if q_temperature is None else (float(q_temperature[0]), float(q_temperature[1]))
+        if self.q_temperature is not None and not self.q_temperature[1] > 0:
+            raise ValueError("gqa_attention: the query temperature's step must be a positive number of positions")
         self.values_are_keys = bool(values_are_keys)
         if self.values_are_keys and ((v_head_dim is not None and v_head_dim != head_dim) or shares_kv):
             raise ValueError("gqa_attention: keys that serve as values have the keys' size and a cache of their own")

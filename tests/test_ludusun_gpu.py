@@ -415,7 +415,7 @@ def test_tensor_core_attention_with_sinks(hd, nh, nkv):
 @pytest.mark.parametrize("nh,nkv,hd,rot,after,temp,same,bias", [
     (4, 2, 16, 8, True, None, False, False), (9, 1, 20, 6, True, None, False, False), (4, 1, 128, 128, True, None, False, False),
     (4, 2, 16, 0, False, (0.3, 5), True, True), (3, 3, 40, 0, False, None, True, True), (16, 1, 64, 0, False, (1.0, 1), True, True),
-    (2, 2, 64, 32, False, (0.5, 64), False, True)])
+    (2, 2, 64, 32, False, (0.5, 64), False, True), (2, 1, 24, 0, False, (0.7, 2.5), True, False)])
 def test_heads_on_their_way_into_the_cache(nh, nkv, hd, rot, after, temp, same, bias):
     """The per-head writer's options, alone and together: heads divided by their root mean square after the rotation (with
     lengthened pairs the order matters), a bias, a query temperature at positions around its steps, rows whose keys are
