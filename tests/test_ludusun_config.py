@@ -225,3 +225,23 @@ def test_plain_model_runs_every_configuration_and_borrowed_keys_matter():
         # causal: a later token changes no earlier row
         lg2 = P.PlainLudusun(cfg, W).logits(toks[:12])
         assert (lg[:12] - lg2).abs().max() < 1e-9
+
+
+def test_a_folder_may_hold_the_second_norm_of_a_layer_without_feed_forward(tmp_path):
+    import os
+    from safetensors.torch import load_file, save_file
+    from rocmforge_b200.config import load_config
+    from rocmforge_b200.weights import WeightError, load_folder
+    write_ludusun(LUDUSUN_CONFIGS["LA"], str(tmp_path), "bfloat16")
+    path = os.path.join(str(tmp_path), "model.safetensors")
+    W = load_file(path)
+    assert "l1.norm2" not in W                                              # layer 1 has no feed-forward
+    W["l1.norm2"] = torch.zeros(64, dtype=torch.bfloat16)
+    save_file(W, path)
+    arch, cfg = load_config(str(tmp_path))
+    specs = arch.build(cfg).param_specs()
+    assert "l1.norm2" in load_folder(str(tmp_path), specs, torch.bfloat16, "cpu")
+    W["l1.mix.v"] = torch.zeros(3, dtype=torch.bfloat16)                    # any other unknown or misshapen tensor is a fault
+    save_file(W, path)
+    with pytest.raises(WeightError):
+        load_folder(str(tmp_path), specs, torch.bfloat16, "cpu")

@@ -412,6 +412,45 @@ def test_tensor_core_attention_with_sinks(hd, nh, nkv):
     assert (got2 - ref[half:]).abs().max() <= 2e-2 * ref.abs().max().clamp(min=1.0)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window,i", [(64, 448), (64, 63), (64, 64), (100, 449), (33, 395), (130, 129), (130, 130), (200, 449), (500, 449)])
+def test_tensor_core_attention_at_a_window_edge_with_a_kv_head_per_head(window, i, hd):
+    """The window of the latent attention on the bfloat16 kernels, as many kv heads as heads: the oldest key of the window
+    stands out and is found, the key just before it stands out more and leaves no trace; the tcgen05 prompt attention
+    (whole prompt, and a second portion whose tiles start in the middle of the sequence) and the clustered decode attention
+    with one to eight CTAs a sequence, against the generic kernel on every row."""
+    from rocmforge_b200 import kernels
+    dev, T, nh = "cuda", 450, 4
+    lo = max(0, i - window + 1)
+    q, k, v = _standing_out(T, i, lo, dev, torch.bfloat16, nh, nh, hd, hd, hidden=[lo - 1] if lo > 0 else [])
+    kp, vp, bt = _paged(k, v)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    q2 = q.reshape(T, nh * hd).contiguous()
+    ref = kernels.attention_generic(q2, nh, nh, hd, kp, vp, seq, pos, zero, bt, 1.0, window).float()
+    assert (ref[i].reshape(nh, hd) - v[lo].float()).abs().max() < 0.05
+    tiles = torch.tensor([[0, r] for r in range(0, T, 128)], dtype=torch.int32, device=dev).flip(0).reshape(-1).contiguous()
+    nnew = torch.tensor([T], dtype=torch.int32, device=dev)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    got = kernels.attention_prefill_tc(q2, nh, nh, hd, kp, vp, tiles, zero, zero, nnew, cu, bt, 1.0, window).float()
+    assert (got - ref).abs().max() <= 2e-2 * ref.abs().max().clamp(min=1.0), f"prompt kernel, window {window}"
+    assert (got[i].reshape(nh, hd) - v[lo].float()).abs().max() < 0.05
+    for j in sorted({i, 70, 200, T - 1}):
+        for splits in (1, 2, 8):
+            one = kernels.attention_decode_warps(q2[j:j + 1].contiguous(), nh, nh, hd, kp, vp, zero, pos[j:j + 1].contiguous(),
+                                                 zero, bt, 1.0, window, splits=splits).float()
+            assert (one[0] - ref[j]).abs().max() <= 2e-2 * ref[j].abs().max().clamp(min=1.0), \
+                f"decode kernel, window {window}, query {j}, {splits} CTAs"
+    half = 201
+    tiles2 = torch.tensor([[0, r] for r in range(0, T - half, 128)], dtype=torch.int32, device=dev).reshape(-1).contiguous()
+    got2 = kernels.attention_prefill_tc(q2[half:].contiguous(), nh, nh, hd, kp, vp, tiles2, zero,
+                                        torch.tensor([half], dtype=torch.int32, device=dev),
+                                        torch.tensor([T - half], dtype=torch.int32, device=dev),
+                                        torch.tensor([0, T - half], dtype=torch.int32, device=dev), bt, 1.0, window).float()
+    assert (got2 - ref[half:]).abs().max() <= 2e-2 * ref.abs().max().clamp(min=1.0)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,rot,after,temp,same,bias", [
     (4, 2, 16, 8, True, None, False, False), (9, 1, 20, 6, True, None, False, False), (4, 1, 128, 128, True, None, False, False),
     (4, 2, 16, 0, False, (0.3, 5), True, True), (3, 3, 40, 0, False, None, True, True), (16, 1, 64, 0, False, (1.0, 1), True, True),
